@@ -1,0 +1,87 @@
+"""A model built from its spec: parts put together, run in the order the schedule gives."""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Union
+
+import torch
+
+from ..parts.base import Part, Runtime, StepContext, part_class
+from ..parts.spec import KvNeed, ModelSpec, PartSpec, StateNeed
+from ..weights.loader import expected_tensors
+
+
+class DecoderModel:
+    """Embedding, blocks, final norm and head of one :class:`ModelSpec`.
+
+    ``weights`` maps checkpoint names to device tensors; tensors are handed to the
+    parts that name them and dropped from the mapping once nobody else needs them, so
+    parts that repack their weights do not keep two copies alive.
+    """
+
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        spec.validate()
+        self.spec, self.rt = spec, rt
+        uses: Dict[str, int] = {}
+        for category, ps in _walk(spec):
+            for name in ps.weights.values():
+                uses[name] = uses.get(name, 0) + 1
+
+        def build(category: str, ps: PartSpec) -> Part:
+            cls = part_class(category, ps.kind)
+            nested = getattr(cls, "nested", {})
+            tensors = {}
+            for local in cls.tensors(ps):
+                tensors[local] = weights[ps.weights[local]]
+            part = cls(ps, tensors, rt, lambda sub, _n=nested, _ps=ps: build(_category_of(_n, _ps, sub), sub))
+            for local in tensors:
+                name = ps.weights[local]
+                uses[name] -= 1
+                if uses[name] <= 0:
+                    weights.pop(name, None)
+            return part
+
+        self.embedding = build("embedding", spec.embedding)
+        self.blocks = [build("block", PartSpec(l.block, l.params, {}, l.parts)) for l in spec.layers]
+        self.final_norm = build("norm", spec.final_norm)
+        self.head = build("head", spec.head)
+        #: what each schedule entry keeps in the cache (None when it keeps nothing of its own)
+        self.needs: List[Union[KvNeed, StateNeed, None]] = []
+        for e in spec.schedule:
+            layer = spec.layers[e.layer]
+            mixer = layer.parts.get("mixer")
+            need = part_class("mixer", mixer.kind).cache_need(mixer) if mixer is not None else None
+            self.needs.append(None if e.cache_of is not None else need)
+
+    def cache_owner(self, entry: int) -> int:
+        e = self.spec.schedule[entry]
+        return entry if e.cache_of is None else e.cache_of
+
+    def forward(self, ctx: StepContext, cache: Any, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
+        """Run the step's tokens through every schedule entry; the float32 logits of
+        the wanted rows ``[n_want, vocab]`` (None when nothing is wanted)."""
+        rt, n = self.rt, ctx.n_tokens
+        x = rt.buffer("residual", (n, self.spec.hidden_size), torch.float32)
+        self.embedding.forward(ctx.tokens, x)
+        for k, e in enumerate(self.spec.schedule):
+            self.blocks[e.layer].forward(x, ctx, cache.view(self.cache_owner(k)), e.cache_of is None)
+        if n_want == 0:
+            return None
+        # the head runs on the wanted rows only (src/lm.rs:114-126)
+        h = rt.buffer("head_in", (n_want, self.spec.hidden_size))
+        self.final_norm.forward(x, h, rows=want_rows)
+        logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        self.head.forward(h, logits)
+        return logits
+
+
+def _category_of(nested: Dict[str, str], parent: PartSpec, sub: PartSpec) -> str:
+    for name, s in parent.parts.items():
+        if s is sub:
+            return nested.get(name, name)
+    raise KeyError("a part built a nested part that its spec does not hold")
+
+
+def _walk(spec: ModelSpec):
+    from ..weights.loader import walk_parts
+    return walk_parts(spec)

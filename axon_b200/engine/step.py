@@ -1,0 +1,156 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes entries ``(slot, tokens, want)``: portions of prompts beside single
+decoded tokens, cut anywhere.  It runs exactly the tokens it is given as one
+flattened batch against what earlier steps left in the cache, and returns the
+float32 logits at the wanted places.  The reference splits this in two calls
+(``feed_slot`` for a prompt portion of one sequence, ``step`` for one row per
+request: src/lm.rs:290-302); here one call holds both, flattened to per-token
+(position, slot) rows like the reference's ``Place::Rows``
+(src/cuda/qwen2/batch.rs:649-671).
+
+A refused step (bad slot, token out of range, no pages) raises before any kernel
+runs, as ``StepError::Input`` does (src/cuda/qwen2/slots.rs:393-438).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import PagedCache
+from ..parts.base import Runtime, StepContext
+from .model import DecoderModel
+
+
+class StepError(ValueError):
+    """The step was refused; nothing ran."""
+
+
+class OutOfPages(StepError):
+    """A request's next tokens need more pages than are free."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    #: places among ``tokens`` whose logits are wanted
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class Engine:
+    """A model, its cache, and the step function over both."""
+
+    def __init__(self, model: DecoderModel, cache: PagedCache, max_step_tokens: int = 8192):
+        self.model, self.cache, self.rt = model, cache, model.rt
+        self.max_step_tokens = max_step_tokens
+        self._staging: List[torch.Tensor] = []
+        self._events: List[Optional[torch.cuda.Event]] = []
+        self._turn = 0
+        #: kernels launched and steps run, for reports
+        self.steps = 0
+
+    # -- requests ---------------------------------------------------------
+    def open_request(self) -> int:
+        slot = self.cache.open()
+        if slot < 0:
+            raise StepError(f"all {self.cache.max_slots} request slots are taken")
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    # -- the step ---------------------------------------------------------
+    def _stage(self, n_ints: int) -> torch.Tensor:
+        """A pinned host buffer that no copy in flight still reads (two take turns)."""
+        if not self._staging:
+            self._staging = [torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32)]
+            self._events = [None, None]
+        i = self._turn
+        self._turn ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        if self._staging[i].numel() < n_ints:
+            self._staging[i] = torch.empty(max(n_ints, 4096), dtype=torch.int32).pin_memory()
+        self._cur = i
+        return self._staging[i]
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        cache, vocab = self.cache, self.model.spec.vocab_size
+        if not entries:
+            return None
+        seen = set()
+        n = 0
+        for e in entries:
+            if not cache.manager.is_open(e.slot):
+                raise StepError(f"slot {e.slot} is not open")
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise StepError(f"slot {e.slot}: an entry needs at least one token")
+            for t in e.tokens:
+                if not (0 <= int(t) < vocab):
+                    raise StepError(f"slot {e.slot}: token {t} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < len(e.tokens)):
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")
+            if cache.length(e.slot) + len(e.tokens) > cache.max_positions:
+                raise StepError(f"slot {e.slot}: {cache.length(e.slot) + len(e.tokens)} positions exceed the "
+                                f"context of {cache.max_positions}")
+            n += len(e.tokens)
+        if n > self.max_step_tokens:
+            raise StepError(f"{n} tokens exceed the step limit of {self.max_step_tokens}")
+
+        # pages for every entry, before anything runs
+        cache.flush()
+        starts = []
+        for e in entries:
+            start = cache.length(e.slot)
+            if not cache.reserve(e.slot, start + len(e.tokens)):
+                raise OutOfPages(f"slot {e.slot}: no pages for positions {start}..{start + len(e.tokens) - 1}")
+            starts.append(start)
+
+        s = len(entries)
+        n_want = sum(len(e.want) for e in entries)
+        total = 3 * n + 4 * s + n_want
+        stage = self._stage(total)
+        buf = stage.numpy()
+        tokens, positions, slots = buf[0:n], buf[n:2 * n], buf[2 * n:3 * n]
+        seg = buf[3 * n:3 * n + 4 * s].reshape(4, s)
+        want = buf[3 * n + 4 * s: total]
+        at = w_at = 0
+        seg_slot, seg_q_start, seg_q_len, seg_kv_len = [], [], [], []
+        for i, (e, start) in enumerate(zip(entries, starts)):
+            k = len(e.tokens)
+            tokens[at:at + k] = np.asarray(e.tokens, dtype=np.int32)
+            positions[at:at + k] = np.arange(start, start + k, dtype=np.int32)
+            slots[at:at + k] = e.slot
+            seg[:, i] = (e.slot, at, k, start + k)
+            seg_slot.append(e.slot); seg_q_start.append(at); seg_q_len.append(k); seg_kv_len.append(start + k)
+            for w in e.want:
+                want[w_at] = at + int(w)
+                w_at += 1
+            at += k
+        dev = self.rt.buffer("step_meta", (total,), torch.int32)
+        dev.copy_(stage[:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[self._cur] = ev
+        cache.sync_tables()
+
+        ctx = StepContext(
+            rt=self.rt, n_tokens=n, tokens=dev[0:n], positions=dev[n:2 * n], token_slot=dev[2 * n:3 * n],
+            seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len,
+            segments=dev[3 * n:3 * n + 4 * s].view(4, s),
+            host_positions=positions.tolist())
+        want_rows = dev[3 * n + 4 * s: total] if n_want else None
+        logits = self.model.forward(ctx, cache, want_rows, n_want)
+        for e, start in zip(entries, starts):
+            cache.commit(e.slot, start + len(e.tokens))
+        self.steps += 1
+        return logits

@@ -1,0 +1,128 @@
+"""Loading the native libraries (building them at first use).
+
+``cuda()`` is the ctypes handle of ``libaxon_cuda.so``; ``host()`` is the
+``axon_host`` extension module.  There is no fallback: when a library cannot be
+built or loaded the error says so and nothing runs.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import threading
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_longlong, c_void_p
+from typing import Any, Optional
+
+_lock = threading.Lock()
+_cuda: Optional[ctypes.CDLL] = None
+_host: Any = None
+
+
+class NativeLibraryError(RuntimeError):
+    """The engine's native code could not be built or loaded."""
+
+
+class KvLayout(ctypes.Structure):
+    """Mirror of ``AxonKvLayout``: where a layer's keys and values lie in its page pool."""
+
+    _fields_ = [
+        ("block_table", c_void_p),
+        ("table_stride", ctypes.c_int32),
+        ("page_size", ctypes.c_int32),
+        ("kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("page_stride", c_int64),
+        ("entry_offset", c_int64),
+        ("v_offset", c_int64),
+    ]
+
+
+P = c_void_p
+_SIGNATURES = {
+    "axon_embed": [P, P, c_int, P, c_int, c_int, c_float, P],
+    "axon_rmsnorm": [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P],
+    "axon_gemm_plain": [P, c_int, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "axon_swiglu": [P, P, c_int, c_int, c_int, P],
+    "axon_rope_table": [P, P, P, c_int, c_int, c_float, P],
+    "axon_rope_kv_write": [P, P, P, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int, c_int, c_int, c_int, c_int, P],
+    "axon_attention_plain": [P, P, c_int, P, P, P, ctypes.POINTER(KvLayout), c_int, c_int, c_float, c_int, P],
+    "axon_residual_add": [P, P, c_int, c_longlong, P],
+    "axon_convert": [P, c_int, P, c_int, c_longlong, P],
+    "axon_argmax": [P, P, c_int, c_int, c_longlong, P],
+    "axon_repeat_penalty": [P, P, P, c_int, c_int, c_longlong, c_int, P],
+    "axon_topk": [P, P, P, P, c_int, c_int, c_longlong, P],
+    "axon_sample_temperature": [P, P, P, P, c_int, c_int, c_longlong, P],
+}
+_OPTIONAL_SIGNATURES: dict = {}
+
+
+def register_signature(name: str, argtypes: list, optional: bool = True) -> None:
+    """Declare a launcher that a kernel module adds to the library."""
+    (_OPTIONAL_SIGNATURES if optional else _SIGNATURES)[name] = argtypes
+    if _cuda is not None:
+        _declare(_cuda, name, argtypes)
+
+
+def _declare(lib: ctypes.CDLL, name: str, argtypes: list) -> None:
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = c_int
+
+
+def cuda() -> ctypes.CDLL:
+    """The CUDA library; built for sm_100a on first use."""
+    global _cuda
+    if _cuda is not None:
+        return _cuda
+    with _lock:
+        if _cuda is not None:
+            return _cuda
+        from ..csrc import build
+        try:
+            path = build.build_cuda()
+            lib = ctypes.CDLL(path)
+        except (build.BuildError, OSError) as e:
+            raise NativeLibraryError(
+                f"axon_b200's CUDA kernels are not available ({e}); there is no fallback path") from e
+        lib.axon_last_error.restype = c_char_p
+        lib.axon_last_error.argtypes = []
+        lib.axon_topk_max.restype = c_int
+        lib.axon_topk_max.argtypes = []
+        for name, sig in list(_SIGNATURES.items()) + list(_OPTIONAL_SIGNATURES.items()):
+            try:
+                _declare(lib, name, sig)
+            except AttributeError:
+                if name in _SIGNATURES:
+                    raise NativeLibraryError(f"libaxon_cuda.so lacks {name}") from None
+        _cuda = lib
+        return lib
+
+
+def host() -> Any:
+    """The host extension module (pages, cache manager, scheduler, sampler)."""
+    global _host
+    if _host is not None:
+        return _host
+    with _lock:
+        if _host is not None:
+            return _host
+        from ..csrc import build
+        try:
+            path = build.build_host()
+            spec = importlib.util.spec_from_file_location("axon_host", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+        except (build.BuildError, ImportError, OSError) as e:
+            raise NativeLibraryError(f"axon_b200's host library is not available ({e})") from e
+        _host = mod
+        return mod
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or the launch failed."""
+
+
+def check(status: int) -> None:
+    if status != 0:
+        msg = cuda().axon_last_error().decode("utf-8", "replace")
+        raise KernelError(msg or f"kernel launcher returned {status}")

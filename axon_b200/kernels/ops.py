@@ -1,0 +1,191 @@
+"""The engine's operations on device tensors, each a hand-written CUDA kernel.
+
+Every function launches on the current CUDA stream and returns nothing: outputs
+are tensors the caller passes in.  Tensors must live on the GPU; there is no CPU
+path.  ``precise=True`` (the 32-bit model) always takes the plain FFMA kernels; the
+bfloat16 model takes the tuned sm_100a kernels where the sizes allow and the plain
+ones otherwise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import lib
+from .lib import KvLayout, check
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"dtype {t.dtype} is not one the kernels take (float32, bfloat16)") from None
+
+
+def _dev(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("kernels take contiguous CUDA tensors; there is no CPU path")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclass
+class KvView:
+    """One schedule entry's keys and values inside its group's page pool.
+
+    ``pool`` is ``[pages + 1][entries][2][kv_heads][page_size][head_dim]`` (the last
+    page is the sink); ``block_table`` is the group's device table
+    ``[slots][stride]`` of int32.
+    """
+
+    pool: torch.Tensor
+    block_table: torch.Tensor
+    entry: int
+    page_size: int
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+    def __post_init__(self) -> None:
+        entries = self.pool.shape[1]
+        plane = self.kv_heads * self.page_size * self.head_dim
+        self.layout = KvLayout(
+            block_table=self.block_table.data_ptr(), table_stride=self.block_table.shape[1],
+            page_size=self.page_size, kv_heads=self.kv_heads, head_dim=self.head_dim,
+            page_stride=entries * 2 * plane, entry_offset=self.entry * 2 * plane, v_offset=plane)
+        self._ref = ctypes.byref(self.layout)
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
+    _dev(tokens, table, x)
+    n, dim = x.shape
+    check(lib.cuda().axon_embed(_ptr(tokens), _ptr(table), dtype_code(table), _ptr(x), n, dim, scale, _stream()))
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None, unit_offset: bool = False) -> None:
+    """out[r] = norm(x[rows[r]] if rows is given else x[r]); x and gain are float32."""
+    _dev(x, gain, out, rows)
+    if x.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise TypeError("rmsnorm reads a float32 residual and a float32 gain")
+    n, dim = out.shape
+    check(lib.cuda().axon_rmsnorm(_ptr(x), _ptr(gain), _ptr(rows), _ptr(out), dtype_code(out), n, dim,
+                                  float(eps), int(unit_offset), _stream()))
+
+
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               accumulate: bool = False) -> None:
+    """out = a @ w.T (+ bias), or out += ... when ``accumulate``; FFMA, any sizes."""
+    _dev(a, w, out, bias)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise ValueError(f"gemm shapes do not fit: a {tuple(a.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise ValueError("a bias is float32 with one value per output column")
+    check(lib.cuda().axon_gemm_plain(_ptr(a), dtype_code(a), _ptr(w), dtype_code(w), _ptr(bias), _ptr(out),
+                                     dtype_code(out), M, N, K, K, N, int(accumulate), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act[t][j] = silu(gate_up[t][2j]) * gate_up[t][2j+1]; gate_up is float32."""
+    _dev(gate_up, act)
+    n, ffn = act.shape
+    if gate_up.dtype != torch.float32 or gate_up.shape != (n, 2 * ffn):
+        raise ValueError("swiglu reads float32 [n][2 * ffn] with gate and up interleaved")
+    check(lib.cuda().axon_swiglu(_ptr(gate_up), _ptr(act), dtype_code(act), n, ffn, _stream()))
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor, magnitude: float = 1.0) -> None:
+    """table[t][i] = (cos, sin)(positions[t] * inv_freq[i]); inv_freq is float64."""
+    _dev(positions, inv_freq, table)
+    n, half = table.shape[0], table.shape[1]
+    if inv_freq.dtype != torch.float64 or inv_freq.numel() != half or table.dtype != torch.float32:
+        raise ValueError("rope_table takes float64 frequencies and writes float32 [n][half][2]")
+    check(lib.cuda().axon_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), n, half, float(magnitude), _stream()))
+
+
+def rope_kv_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions: torch.Tensor,
+                  token_slot: torch.Tensor, q_out: torch.Tensor, kv: KvView, heads: int, rot: int,
+                  adjacent: bool = False, write_kv: bool = True) -> None:
+    _dev(qkv, table, positions, token_slot, q_out, kv.pool)
+    n = q_out.shape[0]
+    if qkv.dtype != torch.float32 or qkv.shape[1] != (heads + 2 * kv.kv_heads) * kv.head_dim:
+        raise ValueError("rope_kv_write reads float32 [n][(heads + 2 kv_heads) * head_dim]")
+    if q_out.dtype != kv.pool.dtype:
+        raise TypeError("queries and the cache have one dtype")
+    check(lib.cuda().axon_rope_kv_write(_ptr(qkv), _ptr(table), _ptr(positions), _ptr(token_slot), _ptr(q_out),
+                                        _ptr(kv.pool), dtype_code(q_out), kv._ref, n, heads, rot, int(adjacent),
+                                        int(write_kv), _stream()))
+
+
+def attention_plain(q: torch.Tensor, kv: KvView, positions: torch.Tensor, token_slot: torch.Tensor,
+                    out: torch.Tensor, heads: int, scale: float) -> None:
+    _dev(q, positions, token_slot, out, kv.pool)
+    n = q.shape[0]
+    if q.dtype != kv.pool.dtype or out.dtype != q.dtype:
+        raise TypeError("queries, cache and output have one dtype")
+    check(lib.cuda().axon_attention_plain(_ptr(q), _ptr(kv.pool), dtype_code(q), _ptr(positions), _ptr(token_slot),
+                                          _ptr(out), kv._ref, n, heads, float(scale), int(kv.window), _stream()))
+
+
+def residual_add(x: torch.Tensor, y: torch.Tensor) -> None:
+    _dev(x, y)
+    if x.dtype != torch.float32 or x.numel() != y.numel():
+        raise ValueError("the residual is float32 and as large as what is added")
+    check(lib.cuda().axon_residual_add(_ptr(x), _ptr(y), dtype_code(y), x.numel(), _stream()))
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _dev(src, dst)
+    if src.numel() != dst.numel():
+        raise ValueError("convert needs equally large tensors")
+    check(lib.cuda().axon_convert(_ptr(src), dtype_code(src), _ptr(dst), dtype_code(dst), src.numel(), _stream()))
+
+
+def argmax(logits: torch.Tensor, best: torch.Tensor) -> None:
+    _dev(logits, best)
+    rows, vocab = logits.shape
+    check(lib.cuda().axon_argmax(_ptr(logits), _ptr(best), rows, vocab, logits.stride(0), _stream()))
+
+
+def repeat_penalty(logits: torch.Tensor, ids: torch.Tensor, penalty: torch.Tensor) -> None:
+    _dev(logits, ids, penalty)
+    rows, vocab = logits.shape
+    check(lib.cuda().axon_repeat_penalty(_ptr(logits), _ptr(ids), _ptr(penalty), rows, vocab, logits.stride(0),
+                                         ids.shape[1], _stream()))
+
+
+def topk_max() -> int:
+    return lib.cuda().axon_topk_max()
+
+
+def topk(logits: torch.Tensor, ks: torch.Tensor, cand_logit: torch.Tensor, cand_id: torch.Tensor) -> None:
+    _dev(logits, ks, cand_logit, cand_id)
+    rows, vocab = logits.shape
+    check(lib.cuda().axon_topk(_ptr(logits), _ptr(ks), _ptr(cand_logit), _ptr(cand_id), rows, vocab,
+                               logits.stride(0), _stream()))
+
+
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+                       picked: torch.Tensor) -> None:
+    _dev(logits, temperature, uniform, picked)
+    rows, vocab = logits.shape
+    if uniform.dtype != torch.float64 or temperature.dtype != torch.float32:
+        raise TypeError("temperatures are float32, uniform numbers float64")
+    check(lib.cuda().axon_sample_temperature(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(picked), rows,
+                                             vocab, logits.stride(0), _stream()))

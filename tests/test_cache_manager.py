@@ -1,0 +1,146 @@
+"""The cache manager on the host: no page is lost, held twice or freed twice, under
+random orders of requests; windows give pages back; tables point at the sink where
+nothing is held (reference: pagemap_fuzz and check(), src/cuda/qwen2/pages.rs:322-438)."""
+
+import random
+
+import numpy as np
+import pytest
+
+from axon_b200.kernels import lib
+
+
+@pytest.fixture(scope="module")
+def host():
+    return lib.host()
+
+
+def test_allocator_basics(host):
+    a = host.PageAllocator(4)
+    pages = [a.alloc() for _ in range(4)]
+    assert pages == [0, 1, 2, 3] and a.alloc() == -1
+    a.release(2)
+    assert a.n_free == 0 and a.n_retired == 1      # two-phase: not free before the flush
+    assert a.alloc() == -1
+    a.flush()
+    assert a.alloc() == 2
+    a.check()
+    with pytest.raises(host.CacheError, match="freed twice"):
+        a.release(1), a.release(1)
+    a.retain(0)
+    a.release(0)
+    assert a.refs(0) == 1
+    a.check()
+
+
+def test_shuffled_hand_out_is_a_permutation(host):
+    a = host.PageAllocator(50, shuffle_seed=7)
+    pages = [a.alloc() for _ in range(50)]
+    assert sorted(pages) == list(range(50)) and pages != list(range(50))
+    b = host.PageAllocator(50, shuffle_seed=7)
+    assert [b.alloc() for _ in range(50)] == pages
+
+
+def test_reserve_is_all_or_nothing_and_tables_follow(host):
+    m = host.CacheManager([host.GroupConfig(4, 6)], max_slots=3, max_positions=40)
+    s = m.open_slot()
+    assert m.reserve(s, 9)                         # 3 pages
+    t = m.table(0)
+    assert t.shape == (3, 10)
+    assert list(t[s, :3]) == [0, 1, 2] and all(t[s, 3:] == m.sink_page(0))
+    s2 = m.open_slot()
+    assert not m.reserve(s2, 13)                   # needs 4, only 3 free: nothing taken
+    assert m.free_pages(0) == 3 and m.slot_pages(0, s2) == 0
+    assert m.pages_short(s2, 13) == 1
+    assert m.reserve(s2, 12)
+    assert m.free_pages(0) == 0
+    m.commit(s, 9)
+    with pytest.raises(host.CacheError, match="without pages"):
+        m.commit(s2, 13)
+    m.close_slot(s)
+    assert m.free_pages(0) == 0 and m.retired_pages(0) == 3
+    m.flush()
+    assert m.free_pages(0) == 3
+    assert all(m.table(0)[s] == m.sink_page(0))
+    with pytest.raises(host.CacheError, match="closed twice"):
+        m.close_slot(s)
+    m.check()
+
+
+def test_window_group_gives_pages_back(host):
+    # group 0 keeps everything, group 1 a window of 6 positions; pages of 4
+    m = host.CacheManager([host.GroupConfig(4, 20), host.GroupConfig(4, 20, 6)], max_slots=2, max_positions=64)
+    s = m.open_slot()
+    length = 0
+    for step in range(30):
+        n = 1 + step % 3
+        assert m.reserve(s, length + n)
+        length += n
+        m.commit(s, length)
+        m.flush()
+        m.check()
+        # the next query (position `length`) sees keys from length - 5: pages before that are gone
+        first_key = max(0, length - 6 + 1)
+        assert m.slot_pages(1, s) == -(-length // 4) - first_key // 4
+        assert m.slot_pages(0, s) == -(-length // 4)
+        t = m.table(1)[s]
+        assert all(t[: first_key // 4] == m.sink_page(1))
+        assert all(t[first_key // 4: -(-length // 4)] != m.sink_page(1))
+    assert m.held_pages(1) <= 3
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_fuzz_random_orders(host, seed):
+    rng = random.Random(seed)
+    groups = [host.GroupConfig(rng.choice([2, 4, 16]), rng.randint(8, 40), rng.choice([0, 0, 5, 17]))
+              for _ in range(rng.randint(1, 3))]
+    # one page size per manager, as the engine builds it
+    ps = groups[0].page_size
+    for g in groups:
+        g.page_size = ps
+    m = host.CacheManager(groups, max_slots=5, max_positions=200, shuffle_seed=seed)
+    live = {}
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.2 and m.n_open < 5:
+            s = m.open_slot()
+            assert s >= 0 and s not in live
+            live[s] = 0
+        elif op < 0.75 and live:
+            s = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 7, 30])
+            if live[s] + n > 200:
+                continue
+            before = [m.free_pages(g) for g in range(m.n_groups)]
+            if m.reserve(s, live[s] + n):
+                live[s] += n
+                m.commit(s, live[s])
+            else:
+                assert [m.free_pages(g) for g in range(m.n_groups)] == before
+        elif op < 0.9 and live:
+            s = rng.choice(list(live))
+            m.close_slot(s)
+            del live[s]
+        else:
+            m.flush()
+        m.check()
+        for s, n in live.items():
+            assert m.length(s) == n
+    for s in list(live):
+        m.close_slot(s)
+    m.flush()
+    m.check()
+    for g in range(m.n_groups):
+        assert m.free_pages(g) == m.group(g).n_pages and m.held_pages(g) == 0
+        assert np.all(m.table(g) == m.sink_page(g))
+
+
+def test_slots_are_reused_and_limited(host):
+    m = host.CacheManager([host.GroupConfig(4, 4)], max_slots=2, max_positions=16)
+    a, b = m.open_slot(), m.open_slot()
+    assert {a, b} == {0, 1} and m.open_slot() == -1
+    m.close_slot(a)
+    assert m.open_slot() == a
+    with pytest.raises(host.CacheError, match="exceeds"):
+        m.reserve(b, 17)
+    assert m.could_ever_hold(16) and not m.could_ever_hold(17)
