@@ -1,0 +1,352 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every
+way of cutting the work: whole prompts, the last 32 tokens one by one, portions of
+changing size down to two tokens, and mixed batches with so few pages that they are
+used again (the reference's batching tests: src/cuda/qwen2/tests.rs:4199-4311,
+src/cuda/qwen2/slots.rs:1622-1796)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from conftest import ROOT, TINY
+
+pytestmark = pytest.mark.gpu
+
+# Largest allowed |engine - plain| as a fraction of the largest |logit| of the request.
+# 32-bit: float rounding through a few layers.  bfloat16: activations are rounded to 8
+# bits of mantissa between kernels.  The mutation checks in test_plain.py show that a
+# wrong formula moves logits by 1e-1 of the scale or more.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+PROMPT_LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 77], "C": [3, 33, 90, 130]}
+
+
+def tokens_for(name, i, n):
+    g = torch.Generator().manual_seed(1000 * (ord(name) - 64) + i)
+    return torch.randint(0, TINY[name]["vocab_size"], (n,), generator=g).tolist()
+
+
+@pytest.fixture(scope="module")
+def plain_models(model_folders):
+    return {k: plain.read_model(v) for k, v in model_folders.items()}
+
+
+@pytest.fixture(scope="module")
+def expected(plain_models):
+    """(name, i) -> float64 logits [T, V] of request i of configuration name."""
+    cache = {}
+
+    def get(name, i, n=None):
+        n = n or PROMPT_LENGTHS[name][i]
+        key = (name, i, n)
+        if key not in cache:
+            cfg, w = plain_models[name]
+            cache[key] = plain.forward(cfg, w, tokens_for(name, i, n))
+        return cache[key]
+    return get
+
+
+def build(folder, dtype, **kw):
+    from axon_b200.engine.build import build_engine
+    kw.setdefault("max_slots", 8)
+    return build_engine(folder, dtype=dtype, **kw)
+
+
+def replay(engine, steps):
+    from axon_b200.engine.replay import Replayer
+    r = Replayer(engine)
+    out = {}
+    for step, logits in r.run(steps):
+        if logits is not None:
+            out[step] = logits.double().cpu()
+    return out
+
+
+def check_rows(got, want_rows, tol, what):
+    """got [n, V] vs the plain rows; error relative to the largest logit."""
+    want = torch.stack(want_rows)
+    scale = float(want.abs().max())
+    err = float((got - want).abs().max())
+    assert got.shape == want.shape, what
+    assert err <= tol * scale, f"{what}: error {err:.3e} is {err / scale:.2e} of the scale (limit {tol:.0e})"
+
+
+def run_and_check(engine, steps, wanted, expected_of, tol, what):
+    """``wanted[step]`` lists (request key, position) in the order the step wants them."""
+    got = replay(engine, steps)
+    assert set(got) == set(wanted), what
+    for step, pairs in wanted.items():
+        rows = [expected_of(*key)[pos] for key, pos in pairs]
+        check_rows(got[step], rows, tol, f"{what}, step {step}")
+
+
+class Trace:
+    """Builds trace steps and remembers which (request, position) each wanted row is."""
+
+    def __init__(self):
+        self.steps, self.wanted, self.pos = [], {}, {}
+
+    def step(self, entries, end=()):
+        k = len(self.steps)
+        rec = {"step": k, "entries": [], "end": list(end)}
+        pairs = []
+        for rid, key, toks, want in entries:
+            start = self.pos.get(rid, 0)
+            rec["entries"].append({"id": rid, "tokens": list(toks), "want": list(want)})
+            pairs += [(key, start + w) for w in want]
+            self.pos[rid] = start + len(toks)
+        for rid in end:
+            self.pos.pop(rid, None)
+        self.steps.append(rec)
+        if pairs:
+            self.wanted[k] = pairs
+        return k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_alone_and_whole(model_folders, expected, name, dtype):
+    engine = build(model_folders[name], dtype, max_tokens=256)
+    for i, n in enumerate(PROMPT_LENGTHS[name]):
+        toks = tokens_for(name, i, n)
+        tr = Trace()
+        tr.step([("r", (name, i), toks, range(n))], end=["r"])
+        run_and_check(engine, tr.steps, tr.wanted, expected, TOL[dtype], f"{name}/{dtype} request {i} whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(model_folders, expected, name, dtype):
+    engine = build(model_folders[name], dtype, max_tokens=256)
+    for i in (2, 3):
+        n = PROMPT_LENGTHS[name][i]
+        toks = tokens_for(name, i, n)
+        head = max(n - 32, 0)
+        tr = Trace()
+        if head:
+            tr.step([("r", (name, i), toks[:head], [head - 1])])
+        for t in range(head, n):
+            tr.step([("r", (name, i), [toks[t]], [0])], end=["r"] if t == n - 1 else [])
+        run_and_check(engine, tr.steps, tr.wanted, expected, TOL[dtype], f"{name}/{dtype} request {i} decoded tail")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("sizes", [[5, 30, 3, 17, 2, 1, 33], [24, 32, 31, 2, 47], [2, 2, 2, 16, 1, 64], [16, 16, 16, 16]])
+def test_portions_of_changing_size(model_folders, expected, name, dtype, sizes):
+    engine = build(model_folders[name], dtype, max_tokens=256, page_size=16)
+    i = 3
+    n = PROMPT_LENGTHS[name][i]
+    toks = tokens_for(name, i, n)
+    tr, at, k = Trace(), 0, 0
+    while at < n:
+        size = min(sizes[k % len(sizes)], n - at)
+        k += 1
+        # ask for the first and the last place of every portion
+        want = sorted({0, size - 1})
+        tr.step([("r", (name, i), toks[at:at + size], want)], end=["r"] if at + size == n else [])
+        at += size
+    run_and_check(engine, tr.steps, tr.wanted, expected, TOL[dtype], f"{name}/{dtype} portions {sizes}")
+
+
+def mixed_trace(name):
+    """Four requests of different lengths: they join at different steps, prompts are fed
+    in portions beside single decoded tokens of others, one is left out of some steps,
+    they end at different steps and a fifth request then takes the pages that came free."""
+    L = PROMPT_LENGTHS[name]
+    lens = {"a": L[3], "b": L[2], "c": L[1] + 20, "d": L[0] + 37, "e": 50}
+    keys = {"a": (name, 3, lens["a"]), "b": (name, 2, lens["b"]), "c": (name, 1, lens["c"]),
+            "d": (name, 0, lens["d"]), "e": (name, 2, lens["e"])}
+    toks = {r: tokens_for(name, keys[r][1], lens[r]) for r in lens}
+    fed = {r: 0 for r in lens}
+    tr = Trace()
+
+    def take(r, k, want_last=True):
+        k = min(k, lens[r] - fed[r])
+        if k <= 0:
+            return None
+        part = toks[r][fed[r]:fed[r] + k]
+        fed[r] += k
+        return (r, keys[r], part, [k - 1] if want_last else [])
+
+    plan = [
+        [("a", 13)],
+        [("a", 2), ("b", 9)],
+        [("a", 1), ("b", 1), ("c", 7)],
+        [("a", 1), ("b", 17), ("c", 1), ("d", 3)],
+        [("a", 30), ("c", 1), ("d", 1)],            # b is left out
+        [("a", 1), ("b", 2), ("c", 5), ("d", 1)],
+    ]
+    for row in plan:
+        ents = [e for e in (take(r, k) for r, k in row) if e]
+        tr.step(ents)
+    # then everyone decodes one token a step until done; finished ones end, and "e" joins
+    # once two of the first four are through, taking pages that came free
+    joined_e = False
+    while any(fed[r] < lens[r] for r in lens):
+        live = [r for r in ("a", "b", "c", "d") if fed[r] < lens[r]]
+        if len(live) <= 2:
+            joined_e = True
+        ents = [take(r, 1) for r in live]
+        if joined_e and fed["e"] < lens["e"]:
+            ents.append(take("e", 11 if fed["e"] < 33 else 1))
+        ending = [e[0] for e in ents if fed[e[0]] == lens[e[0]]]
+        tr.step(ents, end=ending)
+    return tr, keys
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("shuffle", [0, 11])
+def test_mixed_batches_with_pages_used_again(model_folders, plain_models, name, dtype, shuffle):
+    tr, keys = mixed_trace(name)
+    # the pool holds just what is live at the worst moment, so pages must be used again
+    live, worst = {}, 0
+    for rec in tr.steps:
+        for e in rec["entries"]:
+            live[e["id"]] = live.get(e["id"], 0) + len(e["tokens"])
+        worst = max(worst, sum(-(-v // 16) * 16 for v in live.values()))
+        for rid in rec["end"]:
+            live.pop(rid)
+    total = sum(-(-k[2] // 16) * 16 for k in keys.values())
+    assert worst < total, "the trace must need fewer pages than all requests together"
+    engine = build(model_folders[name], dtype, max_tokens=worst, page_size=16, shuffle_seed=shuffle)
+    cfg, w = plain_models[name]
+    full = {}
+
+    def expected_of(nm, i, n):
+        if (nm, i, n) not in full:
+            full[(nm, i, n)] = plain.forward(cfg, w, tokens_for(nm, i, n))
+        return full[(nm, i, n)]
+    run_and_check(engine, tr.steps, tr.wanted, expected_of, TOL[dtype], f"{name}/{dtype} mixed, shuffle {shuffle}")
+    engine.cache.manager.check()
+    engine.cache.flush()
+    assert engine.cache.manager.free_pages(0) == engine.cache.n_pages, "pages were lost"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n", [("A", 128), ("B", 200)])
+def test_long_decoding(model_folders, plain_models, name, dtype, n):
+    engine = build(model_folders[name], dtype, max_tokens=256, page_size=16)
+    cfg, w = plain_models[name]
+    toks = tokens_for(name, 7, n)
+    want = plain.forward(cfg, w, toks)
+    tr = Trace()
+    for t in range(n):
+        tr.step([("r", ("x",), [toks[t]], [0])])
+    got = replay(engine, tr.steps)
+    rows = torch.cat([got[t] for t in range(n)])
+    check_rows(rows, list(want), TOL[dtype], f"{name}/{dtype} {n} tokens one by one")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_folders, plain_models, name, dtype):
+    engine = build(model_folders[name], dtype, max_tokens=128)
+    cfg, w = plain_models[name]
+    for n in (1, 2, 3):
+        toks = tokens_for(name, 20 + n, n)
+        want = plain.forward(cfg, w, toks)
+        tr = Trace()
+        tr.step([("r", ("x",), toks, range(n))], end=["r"])
+        check_rows(replay(engine, tr.steps)[0], list(want), TOL[dtype], f"{name}/{dtype} first {n} tokens")
+
+
+def test_a_far_key_among_hundreds(tmp_path):
+    """One key far back gets a large score for the last query of a long sequence: if a
+    page, a position or a split is wrong anywhere along the way, the output changes by
+    far more than rounding."""
+    from conftest import make_model_folder
+    cfg = dict(TINY["C"], num_hidden_layers=1, max_position_embeddings=1024)
+    folder = make_model_folder(str(tmp_path / "far"), cfg, 77, sharpen=1.0)
+    pcfg, w = plain.read_model(folder)
+    n = 700
+    toks = tokens_for("C", 50, n)
+    # token `needle` appears once, at position 37; the last token is `probe`; make probe's
+    # query and needle's key line up by planting large values in their embedding rows
+    needle, probe = 998, 999
+    toks = [t % 990 for t in toks]
+    toks[37], toks[-1] = needle, probe
+    from safetensors.torch import load_file
+    from axon_b200.weights import write_safetensors
+    t = load_file(os.path.join(folder, "model.safetensors"))
+    e = t["model.embed_tokens.weight"].float()
+    e[needle] = 0
+    e[probe] = 0
+    e[needle, 3] = 4.0
+    e[probe, 3] = 4.0
+    t["model.embed_tokens.weight"] = e.to(torch.bfloat16)
+    for k in ("q_proj", "k_proj"):
+        t[f"model.layers.0.self_attn.{k}.weight"] = (t[f"model.layers.0.self_attn.{k}.weight"].float() * 12).to(torch.bfloat16)
+    write_safetensors(os.path.join(folder, "model.safetensors"), t)
+    pcfg, w = plain.read_model(folder)
+    want = plain.forward(pcfg, w, toks)
+    for dtype in ("float32", "bfloat16"):
+        engine = build(folder, dtype, max_tokens=1024, page_size=16, max_positions=1024)
+        tr = Trace()
+        tr.step([("r", ("x",), toks[:-1], [])])
+        tr.step([("r", ("x",), toks[-1:], [0])], end=["r"])
+        got = replay(engine, tr.steps)[1]
+        check_rows(got, [want[-1]], TOL[dtype], f"far key, {dtype}, decode")
+        tr = Trace()
+        tr.step([("r", ("x",), toks, [n - 1, 37, 38])], end=["r"])
+        got = replay(engine, tr.steps)[0]
+        check_rows(got, [want[-1], want[37], want[38]], TOL[dtype], f"far key, {dtype}, whole")
+
+
+def test_step_refusals(model_folders):
+    from axon_b200.engine.step import OutOfPages, StepEntry, StepError
+    engine = build(model_folders["A"], "float32", max_tokens=32, page_size=16, max_slots=2)
+    s = engine.open_request()
+    with pytest.raises(StepError, match="vocabulary"):
+        engine.step([StepEntry(s, [256], [0])])
+    with pytest.raises(StepError, match="not open"):
+        engine.step([StepEntry(5, [1], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        engine.step([StepEntry(s, [1, 2], [2])])
+    with pytest.raises(StepError, match="twice"):
+        engine.step([StepEntry(s, [1], []), StepEntry(s, [2], [])])
+    assert engine.step([StepEntry(s, list(range(20)), [19])]).shape == (1, 256)
+    s2 = engine.open_request()
+    with pytest.raises(OutOfPages):
+        engine.step([StepEntry(s2, [1], [0])])     # both pages are taken
+    engine.close_request(s)
+    assert engine.step([StepEntry(s2, [1], [0])]).shape == (1, 256)
+    with pytest.raises(StepError, match="slots are taken"):
+        engine.open_request(), engine.open_request()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_folders, plain_models, tmp_path, dtype):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and `done` lines out."""
+    name = "B"
+    cfg, w = plain_models[name]
+    toks = tokens_for(name, 3, 77)
+    want = plain.forward(cfg, w, toks)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": toks[:40], "want": [0, 39]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": toks[40:75], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": toks[75:76], "want": [0]},
+                                {"id": "b", "tokens": toks[:5], "want": [4]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": toks[76:77], "want": [0]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders[name], "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", "192"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert not (out / "1.f32").exists()
+    V = cfg["vocab_size"]
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V)).double()
+    check_rows(got0, [want[0], want[39]], TOL[dtype], "trace_run step 0")
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, V)).double()
+    check_rows(got2, [want[75], want[4]], TOL[dtype], "trace_run step 2")
+    got3 = torch.from_numpy(np.fromfile(out / "3.f32", dtype="<f4").reshape(-1, V)).double()
+    check_rows(got3, [want[76]], TOL[dtype], "trace_run step 3")
