@@ -1,0 +1,312 @@
+"""Each kernel alone against a plain PyTorch float32/float64 statement of the same op,
+at sizes other than the engine tests' (widths and vocabularies that are no power of
+two, head sizes in steps of 16, any number of heads and groups), with pages handed
+out in a shuffled order (reference: src/cuda/qwen2/tests.rs:1076-1503,
+src/cuda/qwen2/paged_tests.rs:216,609)."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+# products and sums of bfloat16 inputs are exact in float32; what differs from the
+# float64 statement is the rounding of the *output* (and of float32 accumulation)
+OUT_TOL = {torch.float32: 2e-5, torch.bfloat16: 1e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from axon_b200.kernels import ops as o
+    return o
+
+
+def close(got, want, tol, what=""):
+    want = want.to(torch.float64)
+    scale = max(float(want.abs().max()), 1e-6)
+    err = float((got.to(torch.float64) - want).abs().max())
+    assert err <= tol * scale, f"{what}: error {err:.3e} = {err / scale:.2e} of scale (limit {tol:.0e})"
+
+
+def rand(*shape, dtype=torch.float32, seed=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, dtype):
+    table = rand(37, 50, dtype=dtype)
+    tokens = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    x = torch.empty(5, 50, dtype=torch.float32, device=DEV)
+    ops.embed(tokens, table, x, scale=1.0)
+    assert torch.equal(x, table[tokens.long()].float())
+    ops.embed(tokens, table, x, scale=3.0)
+    assert torch.equal(x, table[tokens.long()].float() * 3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim", [1, 50, 96, 1000, 3584 + 8])
+def test_rmsnorm(ops, dtype, dim):
+    x = rand(9, dim, seed=1, std=3.0)
+    gain = rand(dim, seed=2) * 0.1 + 1.0
+    out = torch.empty(9, dim, dtype=dtype, device=DEV)
+    for eps in (1e-6, 0.5):
+        ops.rmsnorm(x, gain, out, eps)
+        xd = x.double()
+        want = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * gain.double()
+        close(out, want, OUT_TOL[dtype], f"rmsnorm dim {dim} eps {eps}")
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(3, dim, dtype=dtype, device=DEV)
+    ops.rmsnorm(x, gain, out3, 1e-6, rows=rows)
+    assert torch.equal(out3, _norm_rows(ops, x, gain, rows, dtype, dim)), "gathered rows differ from their norms"
+    ops.rmsnorm(x, gain - 1.0, out, 1e-6, unit_offset=True)
+    xd = x.double()
+    close(out, xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-6) * gain.double(), OUT_TOL[dtype], "1 + w gain")
+
+
+def _norm_rows(ops, x, gain, rows, dtype, dim):
+    full = torch.empty(x.shape[0], dim, dtype=dtype, device=DEV)
+    ops.rmsnorm(x, gain, full, 1e-6)
+    return full[rows.long()]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (1, 33, 5), (7, 200, 64), (65, 129, 97), (130, 64, 256), (3, 1000, 160)])
+def test_gemm_plain(ops, dtype, M, N, K):
+    a, w = rand(M, K, dtype=dtype, seed=3), rand(N, K, dtype=dtype, seed=4, std=0.2)
+    bias = rand(N, seed=5)
+    want = a.double() @ w.double().T
+    for out_dtype in (torch.float32, dtype):
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.gemm_plain(a, w, out)
+        close(out, want, OUT_TOL[out_dtype], f"gemm {M}x{N}x{K}")
+        ops.gemm_plain(a, w, out, bias=bias)
+        close(out, want + bias.double(), OUT_TOL[out_dtype], "gemm + bias")
+    res = rand(M, N, seed=6)
+    acc = res.clone()
+    ops.gemm_plain(a, w, acc, accumulate=True)
+    close(acc, want + res.double(), OUT_TOL[torch.float32], "gemm into the residual")
+
+
+def test_gemm_plain_mixed_dtypes(ops):
+    a, w = rand(5, 40, dtype=torch.bfloat16, seed=7), rand(9, 40, seed=8)
+    out = torch.empty(5, 9, dtype=torch.float32, device=DEV)
+    ops.gemm_plain(a, w, out)       # a matrix stored in 32-bit under bfloat16 activations
+    close(out, a.double() @ w.double().T, 2e-5)
+
+
+def test_gemm_refuses_bad_shapes(ops):
+    a, w = rand(4, 8), rand(5, 9)
+    with pytest.raises(ValueError, match="shapes"):
+        ops.gemm_plain(a, w, torch.empty(4, 5, device=DEV))
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.gemm_plain(a.cpu(), w.cpu(), torch.empty(4, 5))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    n, f = 6, 75
+    gu = rand(n, 2 * f, seed=9, std=2.0)
+    act = torch.empty(n, f, dtype=dtype, device=DEV)
+    ops.swiglu(gu, act)
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()
+    close(act, g / (1 + torch.exp(-g)) * u, OUT_TOL[dtype], "swiglu")
+
+
+@pytest.mark.parametrize("half,theta", [(8, 1e4), (64, 1e6), (24, 5e5)])
+def test_rope_table(ops, half, theta):
+    pos = torch.tensor([0, 1, 17, 4095, 131071], dtype=torch.int32, device=DEV)
+    inv = torch.tensor([theta ** (-2.0 * i / (2 * half)) for i in range(half)], dtype=torch.float64, device=DEV)
+    table = torch.empty(5, half, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(pos, inv, table)
+    ang = pos.double()[:, None] * inv[None, :]
+    # the angle is exact in float64 and rounded to float32 once: half an ulp of error
+    assert float((table[..., 0].double() - torch.cos(ang)).abs().max()) <= 6e-8
+    assert float((table[..., 1].double() - torch.sin(ang)).abs().max()) <= 6e-8
+
+
+def make_cache(ops, dtype, kv_heads, head_dim, page_size, n_pages, slots, max_pos, entries=2, entry=1, window=0, seed=0):
+    """A pool with pages handed out in a shuffled order, and its table."""
+    stride = -(-max_pos // page_size)
+    pool = torch.zeros(n_pages + 1, entries, 2, kv_heads, page_size, head_dim, dtype=dtype, device=DEV)
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)
+    table = torch.full((slots, stride), n_pages, dtype=torch.int32)
+    at = 0
+    for s in range(slots):
+        for lp in range(stride):
+            if at < n_pages:
+                table[s, lp] = perm[at]
+                at += 1
+    table = table.to(DEV)
+    return ops.KvView(pool, table, entry, page_size, kv_heads, head_dim, window), table
+
+
+def read_cache(view, table, slot, pos, which):
+    ps = view.page_size
+    page = int(table[slot, pos // ps])
+    return view.pool[page, view.entry, which, :, pos % ps, :]     # [kv_heads, head_dim]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,rot,adjacent", [(4, 2, 16, 16, False), (3, 1, 32, 32, True),
+                                                            (6, 3, 48, 16, False), (2, 2, 128, 0, False)])
+def test_rope_kv_write(ops, dtype, heads, kv_heads, hd, rot, adjacent):
+    n, ps = 11, 4
+    view, table = make_cache(ops, dtype, kv_heads, hd, ps, 12, 2, 24, seed=5)
+    qkv = rand(n, (heads + 2 * kv_heads) * hd, seed=11)
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 9, 10, 11, 12], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32, device=DEV)
+    tab = None
+    if rot:
+        inv = torch.tensor([1e4 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64, device=DEV)
+        tab = torch.empty(n, rot // 2, 2, dtype=torch.float32, device=DEV)
+        ops.rope_table(positions, inv, tab)
+    q_out = torch.empty(n, heads * hd, dtype=dtype, device=DEV)
+    ops.rope_kv_write(qkv, tab, positions, slots, q_out, view, heads, rot, adjacent)
+
+    def rotate(v, t):      # v [..., hd] float64
+        if not rot:
+            return v
+        out = v.clone()
+        c, s = tab[t, :, 0].double(), tab[t, :, 1].double()
+        if adjacent:
+            a, b = v[..., 0:rot:2], v[..., 1:rot:2]
+            out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = v[..., :rot // 2], v[..., rot // 2:rot]
+            out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * s, a * s + b * c
+        return out
+
+    q = qkv[:, :heads * hd].double().view(n, heads, hd)
+    k = qkv[:, heads * hd:(heads + kv_heads) * hd].double().view(n, kv_heads, hd)
+    v = qkv[:, (heads + kv_heads) * hd:].double().view(n, kv_heads, hd)
+    for t in range(n):
+        close(q_out[t].view(heads, hd), rotate(q[t], t), OUT_TOL[dtype], "q")
+        close(read_cache(view, table, int(slots[t]), int(positions[t]), 0), rotate(k[t], t), OUT_TOL[dtype], "k page")
+        close(read_cache(view, table, int(slots[t]), int(positions[t]), 1), v[t], OUT_TOL[dtype], "v page")
+    # the other plane of the pool (another layer's) was not touched
+    assert float(view.pool[:, 0].abs().max()) == 0.0
+    # write_kv off leaves the cache alone
+    before = view.pool.clone()
+    ops.rope_kv_write(qkv * 2, tab, positions, slots, q_out, view, heads, rot, adjacent, write_kv=False)
+    assert torch.equal(before, view.pool)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,ps,window", [(4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (7, 7, 48, 8, 0),
+                                                         (8, 2, 128, 16, 0), (2, 1, 256, 16, 0), (4, 2, 64, 4, 5)])
+def test_attention_plain(ops, dtype, heads, kv_heads, hd, ps, window):
+    lens = [37, 70]                  # two requests of different lengths
+    n_pages = 2 * -(-80 // ps)      # make_cache fills every table entry of both slots
+    view, table = make_cache(ops, dtype, kv_heads, hd, ps, n_pages, 2, 80, window=window, seed=9)
+    ks = [rand(l, kv_heads, hd, dtype=dtype, seed=20 + i) for i, l in enumerate(lens)]
+    vs = [rand(l, kv_heads, hd, dtype=dtype, seed=30 + i) for i, l in enumerate(lens)]
+    for s, l in enumerate(lens):
+        for p in range(l):
+            page = int(table[s, p // ps])
+            view.pool[page, view.entry, 0, :, p % ps, :] = ks[s][p]
+            view.pool[page, view.entry, 1, :, p % ps, :] = vs[s][p]
+    # queries: the last 5 positions of request 0 and positions 0, 1, 33 and the last of request 1
+    qpos = [(0, p) for p in range(32, 37)] + [(1, 0), (1, 1), (1, 33), (1, 69)]
+    q = rand(len(qpos), heads * hd, dtype=dtype, seed=40)
+    positions = torch.tensor([p for _, p in qpos], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([s for s, _ in qpos], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention_plain(q, view, positions, slots, out, heads, scale)
+    group = heads // kv_heads
+    for i, (s, p) in enumerate(qpos):
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(heads):
+            qh = q[i].view(heads, hd)[h].double()
+            kk, vv = ks[s][lo:p + 1, h // group].double(), vs[s][lo:p + 1, h // group].double()
+            w = torch.softmax((kk @ qh) * scale, dim=0)
+            close(out[i].view(heads, hd)[h], w @ vv, OUT_TOL[dtype], f"attention query {i} head {h}")
+
+
+def test_argmax_rule(ops):
+    row = torch.zeros(4, 1003, dtype=torch.float32, device=DEV)
+    row[0, 17] = 5.0; row[0, 900] = 5.0            # equal maxima: the last index
+    row[1, :] = -1.0; row[1, 3] = float("nan")     # NaN is never picked
+    row[1, 44] = -0.5
+    row[2, :] = float("nan")                        # all NaN: the last index
+    row[3, 0] = 0.0; row[3, 5] = -0.0               # -0 ties +0: larger id among them
+    row[3, 6:] = -1.0
+    best = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.argmax(row, best)
+    assert best.tolist() == [900, 44, 1002, 5]
+    big = rand(3, 152064, seed=50)
+    best = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(big, best)
+    assert best.tolist() == big.argmax(dim=1).tolist()
+
+
+@pytest.mark.parametrize("vocab", [300, 1000, 152064])
+def test_topk_and_penalty(ops, vocab):
+    logits = rand(3, vocab, seed=51, std=3.0)
+    logits[1, 7] = logits[1, 9] = logits[1].max() + 1.0         # a tie at the top: larger id first
+    logits[2, 5] = float("nan")
+    ks = torch.tensor([40, 256, 3], dtype=torch.int32, device=DEV)
+    cl = torch.empty(3, 256, dtype=torch.float32, device=DEV)
+    ci = torch.empty(3, 256, dtype=torch.int32, device=DEV)
+    ops.topk(logits, ks, cl, ci)
+    for r, k in enumerate(ks.tolist()):
+        row = logits[r].clone()
+        row[row != row] = -float("inf")
+        key = row.double().cpu()
+        order = sorted(range(vocab), key=lambda i: (key[i].item(), i), reverse=True)[:k]
+        assert ci[r, :k].tolist() == order
+        assert torch.equal(cl[r, :k].cpu(), logits[r].cpu()[order])
+    ids = torch.tensor([[1, 2, -1], [7, -1, -1], [0, 1, 2]], dtype=torch.int32, device=DEV)
+    pen = torch.tensor([1.5, 1.0, 2.0], dtype=torch.float32, device=DEV)
+    before = logits.clone()
+    ops.repeat_penalty(logits, ids, pen)
+    for r in range(3):
+        for j in ids[r].tolist():
+            if j < 0:
+                continue
+            b = before[r, j]
+            want = b if pen[r] == 1.0 else (b / pen[r] if b > 0 else b * pen[r])
+            assert logits[r, j] == want
+    untouched = torch.ones_like(logits, dtype=torch.bool)
+    for r in range(3):
+        for j in ids[r].tolist():
+            if j >= 0:
+                untouched[r, j] = False
+    same = (logits == before) | (logits != logits)
+    assert bool(same[untouched].all())
+
+
+def test_sample_temperature(ops):
+    vocab = 1000
+    p = torch.softmax(rand(vocab, seed=52, std=2.0).double(), 0)
+    logits = torch.log(p).float().repeat(4000, 1).contiguous()
+    temps = torch.full((4000,), 1.0, dtype=torch.float32, device=DEV)
+    g = torch.Generator().manual_seed(1)
+    us = torch.rand(4000, generator=g, dtype=torch.float64).to(DEV)
+    picked = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, temps, us, picked)
+    # each pick is the inverse CDF at its u, ids ascending
+    cdf = torch.cumsum(p, 0)
+    want = torch.searchsorted(cdf, us * cdf[-1], right=True).clamp(max=vocab - 1)
+    agree = (picked.long() == want).float().mean().item()
+    assert agree > 0.995, f"only {agree:.4f} of the picks match the inverse CDF"   # float32 weights vs float64 cdf
+    # a low temperature concentrates on the best token
+    temps.fill_(0.05)
+    ops.sample_temperature(logits, temps, us, picked)
+    assert (picked.long() == int(p.argmax())).float().mean().item() > 0.95
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_residual_add_and_convert(ops, dtype):
+    x, y = rand(7, 33, seed=60), rand(7, 33, dtype=dtype, seed=61)
+    want = x + y.float()
+    ops.residual_add(x, y)
+    assert torch.equal(x, want)
+    out = torch.empty(7, 33, dtype=dtype, device=DEV)
+    ops.convert(x, out)
+    assert torch.equal(out, x.to(dtype))

@@ -1,0 +1,348 @@
+"""Each part alone against its plain statement, and the generality of the layout: a
+toy architecture defined here (a mixer with state of its own, a windowed attention
+with adjacent-pair rotation, a layer that runs twice, a layer that reads another
+layer's cache) is registered, written as a random model folder, built and stepped
+without a change to the framework's files."""
+
+import math
+from dataclasses import dataclass
+from typing import ClassVar, Tuple
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float32: 2e-5, torch.bfloat16: 3e-2}
+
+
+def close(got, want, tol, what=""):
+    want = want.to(torch.float64).cpu()
+    scale = max(float(want.abs().max()), 1e-6)
+    err = float((got.to(torch.float64).cpu() - want).abs().max())
+    assert err <= tol * scale, f"{what}: error {err:.3e} = {err / scale:.2e} of scale (limit {tol:.0e})"
+
+
+def rand(*shape, seed=0, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+def make_ctx(rt, cache, segs, tokens=None):
+    """A StepContext for segments [(slot, n_tokens)], continuing what each slot holds."""
+    from axon_b200.parts import StepContext
+    pos, slot_of, seg = [], [], [[], [], [], []]
+    at = 0
+    for slot, n in segs:
+        start = cache.length(slot)
+        assert cache.reserve(slot, start + n)
+        pos += list(range(start, start + n))
+        slot_of += [slot] * n
+        for lst, v in zip(seg, (slot, at, n, start + n)):
+            lst.append(v)
+        at += n
+    cache.sync_tables()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    ctx = StepContext(rt=rt, n_tokens=at, tokens=i32(tokens if tokens is not None else [0] * at), positions=i32(pos),
+                      token_slot=i32(slot_of), seg_slot=seg[0], seg_q_start=seg[1], seg_q_len=seg[2],
+                      seg_kv_len=seg[3], segments=i32(seg), host_positions=pos)
+    return ctx
+
+
+def commit(cache, ctx):
+    for slot, kv in zip(ctx.seg_slot, ctx.seg_kv_len):
+        cache.commit(slot, kv)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_embedding_head_parts(dtype):
+    from axon_b200.parts import PartSpec, Runtime, part_class
+    rt = Runtime(dtype, DEV)
+    gain = rand(70, seed=1) * 0.1 + 1
+    norm = part_class("norm", "rmsnorm")(PartSpec("rmsnorm", {"size": 70, "eps": 1e-3}, {"gain": "g"}), {"gain": gain}, rt, None)
+    x = rand(5, 70, seed=2, std=4.0)
+    out = torch.empty(5, 70, dtype=dtype, device=DEV)
+    norm.forward(x, out)
+    close(out, plain.rms_norm(x.double().cpu(), gain.double().cpu(), 1e-3), TOL[dtype], "rmsnorm part")
+
+    table = rand(33, 70, seed=3, dtype=dtype)
+    emb = part_class("embedding", "embedding")(PartSpec("embedding", {"vocab_size": 33, "hidden_size": 70}, {"table": "t"}),
+                                               {"table": table}, rt, None)
+    tok = torch.tensor([32, 0, 7], dtype=torch.int32, device=DEV)
+    x3 = torch.empty(3, 70, dtype=torch.float32, device=DEV)
+    emb.forward(tok, x3)
+    assert torch.equal(x3.cpu(), plain.embed(table.double().cpu(), [32, 0, 7]).float())
+
+    head = part_class("head", "linear_head")(PartSpec("linear_head", {"vocab_size": 33, "hidden_size": 70}, {"weight": "t"}),
+                                             {"weight": table}, rt, None)
+    h = rand(3, 70, seed=4, dtype=dtype)
+    logits = torch.empty(3, 33, dtype=torch.float32, device=DEV)
+    head.forward(h, logits)
+    close(logits, plain.linear(h.double().cpu(), table.double().cpu()), 2e-5 if dtype == torch.float32 else 1e-2, "head part")
+
+
+def test_rope_part_tables_are_shared_per_step():
+    from axon_b200.cache import PagedCache
+    from axon_b200.parts import KvNeed, PartSpec, Runtime, part_class
+    rt = Runtime(torch.float32, DEV)
+    cache = PagedCache([KvNeed(1, 16)], torch.float32, DEV, page_size=4, max_tokens=64, max_slots=2, max_positions=64)
+    s = cache.open()
+    ctx = make_ctx(rt, cache, [(s, 6)])
+    spec = PartSpec("rope", {"head_dim": 16, "theta": 1e4, "pairing": "half"})
+    a = part_class("position", "rope")(spec, {}, rt, None)
+    b = part_class("position", "rope")(spec, {}, rt, None)
+    other = part_class("position", "rope")(PartSpec("rope", {"head_dim": 16, "theta": 1e6, "pairing": "adjacent", "rot": 8}), {}, rt, None)
+    ta, tb, tc = a.rotation(ctx), b.rotation(ctx), other.rotation(ctx)
+    assert ta.data_ptr() == tb.data_ptr() and tc.data_ptr() != ta.data_ptr()
+    assert ta.shape == (6, 8, 2) and tc.shape == (6, 4, 2) and other.adjacent and other.rot == 8
+    ang = torch.arange(6, dtype=torch.float64)[:, None] * torch.tensor([1e4 ** (-2 * i / 16) for i in range(8)], dtype=torch.float64)
+    assert float((ta[..., 0].double().cpu() - torch.cos(ang)).abs().max()) < 6e-8
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,hd,window", [(4, 2, 16, None), (5, 5, 32, None), (6, 2, 64, 7)])
+def test_attention_part_alone(dtype, heads, kv_heads, hd, window):
+    """The mixer by itself: whole sequence in one step, then the same sequence in
+    portions, against q/k/v + RoPE + attention + o written with the plain functions."""
+    from axon_b200.cache import PagedCache
+    from axon_b200.parts import PartSpec, Runtime, part_class
+    D, T = 72, 29
+    rt = Runtime(dtype, DEV)
+    spec = PartSpec("attention", {"hidden_size": D, "heads": heads, "kv_heads": kv_heads, "head_dim": hd,
+                                  "qkv_bias": True, "out_bias": False, "window": window, "scale": None},
+                    {k: k for k in ("q", "k", "v", "o", "q_bias", "k_bias", "v_bias")},
+                    {"position": PartSpec("rope", {"head_dim": hd, "theta": 1e4, "pairing": "half"})})
+    cls = part_class("mixer", "attention")
+    w = {}
+    for i, (name, decl) in enumerate(cls.tensors(spec).items()):
+        vec = decl.kind == "bias"
+        w[name] = rand(*decl.shape, seed=100 + i, std=0.3, dtype=torch.float32 if vec else dtype)
+    ref = {k: v.double().cpu() for k, v in w.items()}
+    from axon_b200.engine.model import DecoderModel  # noqa: F401  (registers nothing; parts are built directly)
+    mixer = cls(spec, dict(w), rt, lambda sub: part_class("position", sub.kind)(sub, {}, rt, None))
+    cache = PagedCache([cls.cache_need(spec)], dtype, DEV, page_size=4, max_tokens=64, max_slots=2, max_positions=64,
+                       shuffle_seed=3)
+    h = rand(T, D, seed=7, dtype=dtype)
+    hd64 = h.double().cpu()
+    q = plain.linear(hd64, ref["q"], ref["q_bias"]).view(T, heads, hd)
+    k = plain.linear(hd64, ref["k"], ref["k_bias"]).view(T, kv_heads, hd)
+    v = plain.linear(hd64, ref["v"], ref["v_bias"]).view(T, kv_heads, hd)
+    q, k = plain.rope_half(q, range(T), 1e4), plain.rope_half(k, range(T), 1e4)
+    want = plain.linear(plain.causal_gqa_attention(q, k, v, window=window).reshape(T, heads * hd), ref["o"])
+    for cuts in ([T], [5, 1, 1, 16, 2, 4]):
+        s = cache.open()
+        x = torch.zeros(T, D, dtype=torch.float32, device=DEV)
+        at = 0
+        for n in cuts:
+            cache.flush()
+            ctx = make_ctx(rt, cache, [(s, n)])
+            xs = x[at:at + n]
+            mixer.forward(h[at:at + n].contiguous(), xs, ctx, cache.view(0), True)
+            commit(cache, ctx)
+            at += n
+        close(x, want, TOL[dtype], f"attention part, cuts {cuts}")
+        cache.close(s)
+    if window:
+        assert cache.manager.held_pages(0) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part_and_block(dtype):
+    from axon_b200.cache import PagedCache
+    from axon_b200.parts import PartSpec, Runtime, part_class
+    D, F, T = 48, 100, 9
+    rt = Runtime(dtype, DEV)
+    fspec = PartSpec("swiglu", {"hidden_size": D, "intermediate_size": F}, {k: k for k in ("gate", "up", "down")})
+    fw = {k: rand(*s, seed=10 + i, std=0.2, dtype=dtype) for i, (k, s) in enumerate(
+        {"gate": (F, D), "up": (F, D), "down": (D, F)}.items())}
+    ffn = part_class("ffn", "swiglu")(fspec, dict(fw), rt, None)
+    h = rand(T, D, seed=20, dtype=dtype)
+    x0 = rand(T, D, seed=21)
+    x = x0.clone()
+    ffn.forward(h, x, None)
+    want = x0.double().cpu() + plain.swiglu_ffn(h.double().cpu(), *(fw[k].double().cpu() for k in ("gate", "up", "down")))
+    close(x, want, TOL[dtype], "swiglu part adds into the residual")
+
+
+# ---------------------------------------------------------------------------
+# A toy architecture, defined and registered here.
+
+def register_toy():
+    from axon_b200.config.base import ModelConfig, register_architecture
+    from axon_b200.parts import (LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry, StateNeed, TensorDecl,
+                                 register_part)
+
+    @register_part
+    class RunningMean(Mixer):
+        """out_t = W mean(h_0..h_t): state of fixed size (the running sum and the count)."""
+        category, kind = "mixer", "toy_running_mean"
+
+        @classmethod
+        def tensors(cls, spec):
+            d = spec.params["hidden_size"]
+            return {"w": TensorDecl((d, d))}
+
+        @classmethod
+        def cache_need(cls, spec):
+            return StateNeed((spec.params["hidden_size"] + 1,), "float32")
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            self.w, self.d = tensors["w"], spec.params["hidden_size"]
+
+        def compute(self, h, ctx, state):
+            out = torch.empty(h.shape[0], self.d, dtype=torch.float32, device=h.device)
+            for slot, at, n in zip(ctx.seg_slot, ctx.seg_q_start, ctx.seg_q_len):
+                hs = h[at:at + n].float()
+                total = state[slot, :self.d] + torch.cumsum(hs, 0)
+                count = state[slot, self.d] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)
+                state[slot, :self.d] = total[-1]
+                state[slot, self.d] = count[-1]
+                out[at:at + n] = (total / count[:, None]) @ self.w.float().T
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyForCausalLM"
+        model_types: ClassVar[Tuple[str, ...]] = ("toy_test",)
+        hidden_size: int = 40
+        vocab_size: int = 99
+        heads: int = 4
+        kv_heads: int = 2
+        head_dim: int = 16
+        ffn: int = 56
+        window: int = 6
+        eps: float = 1e-5
+        max_positions: int = 96
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg})
+
+    def toy_spec(c):
+        norm = lambda name: PartSpec("rmsnorm", {"size": c.hidden_size, "eps": c.eps}, {"gain": name})
+
+        def attn(p, window, pairing, theta):
+            return PartSpec("attention", {"hidden_size": c.hidden_size, "heads": c.heads, "kv_heads": c.kv_heads,
+                                          "head_dim": c.head_dim, "qkv_bias": False, "out_bias": False,
+                                          "window": window, "scale": None},
+                            {k: f"{p}.{k}" for k in ("q", "k", "v", "o")},
+                            {"position": PartSpec("rope", {"head_dim": c.head_dim, "theta": theta, "pairing": pairing})})
+
+        def ffn(p):
+            return PartSpec("swiglu", {"hidden_size": c.hidden_size, "intermediate_size": c.ffn},
+                            {k: f"{p}.{k}" for k in ("gate", "up", "down")})
+
+        def layer(i, mixer):
+            return LayerSpec("prenorm", {"norm_mixer": norm(f"l{i}.n1"), "mixer": mixer,
+                                         "norm_ffn": norm(f"l{i}.n2"), "ffn": ffn(f"l{i}.ffn")})
+        layers = (
+            layer(0, attn("l0.attn", c.window, "adjacent", 1e4)),            # windowed, adjacent pairs
+            layer(1, PartSpec("toy_running_mean", {"hidden_size": c.hidden_size}, {"w": "l1.mean.w"})),
+            layer(2, attn("l2.attn", None, "half", 1e5)),                    # full attention
+            layer(3, attn("l3.attn", None, "half", 1e5)),                    # reads layer 2's cache
+        )
+        # layer 0 runs twice (each run with a cache of its own); the last entry reads entry 3's cache
+        schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2), ScheduleEntry(3, cache_of=3))
+        return ModelSpec("ToyForCausalLM", c.hidden_size, c.vocab_size, c.max_positions,
+                         PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"table": "embed"}),
+                         layers, schedule, norm("final"),
+                         PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"weight": "head"}))
+
+    register_architecture(ToyConfig, toy_spec)
+    return ToyConfig
+
+
+def rope_adjacent(v, positions, theta):
+    """Pairs (2i, 2i+1) rotate by pos * theta^(-2i/hd)."""
+    hd = v.shape[-1]
+    freq = torch.tensor([theta ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64)
+    ang = torch.tensor(list(positions), dtype=torch.float64)[:, None] * freq[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = v[..., 0::2], v[..., 1::2]
+    out = torch.empty_like(v)
+    out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+    return out
+
+
+def toy_plain_forward(c, w, tokens):
+    """The toy architecture written with the plain functions, whole sequence, no cache."""
+    T = len(tokens)
+    pos = list(range(T))
+    x = plain.embed(w["embed"], tokens)
+
+    def attn_layer(x, i, window, rope, theta, kv_from=None):
+        h = plain.rms_norm(x, w[f"l{i}.n1"], c.eps)
+        q = plain.linear(h, w[f"l{i}.attn.q"]).view(T, c.heads, c.head_dim)
+        k = plain.linear(h, w[f"l{i}.attn.k"]).view(T, c.kv_heads, c.head_dim)
+        v = plain.linear(h, w[f"l{i}.attn.v"]).view(T, c.kv_heads, c.head_dim)
+        q, k = rope(q, pos, theta), rope(k, pos, theta)
+        kv = (k, v)
+        if kv_from is not None:
+            k, v = kv_from
+        o = plain.causal_gqa_attention(q, k, v, window=window).reshape(T, c.heads * c.head_dim)
+        x = x + plain.linear(o, w[f"l{i}.attn.o"])
+        return ffn_half(x, i), kv
+
+    def ffn_half(x, i):
+        h = plain.rms_norm(x, w[f"l{i}.n2"], c.eps)
+        return x + plain.swiglu_ffn(h, w[f"l{i}.ffn.gate"], w[f"l{i}.ffn.up"], w[f"l{i}.ffn.down"])
+
+    x, _ = attn_layer(x, 0, c.window, rope_adjacent, 1e4)
+    h = plain.rms_norm(x, w["l1.n1"], c.eps)
+    mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+    x = ffn_half(x + plain.linear(mean, w["l1.mean.w"]), 1)
+    x, _ = attn_layer(x, 0, c.window, rope_adjacent, 1e4)
+    x, kv2 = attn_layer(x, 2, None, plain.rope_half, 1e5)
+    x, _ = attn_layer(x, 3, None, plain.rope_half, 1e5, kv_from=kv2)
+    return plain.linear(plain.rms_norm(x, w["final"], c.eps), w["head"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
+    from safetensors.torch import load_file
+
+    from axon_b200.engine.build import build_engine
+    from axon_b200.engine.replay import Replayer
+    from axon_b200.weights import write_random_model, write_safetensors
+    ToyConfig = register_toy()
+    cfg = ToyConfig()
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, cfg, seed=5, std=0.12)
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    engine = build_engine(folder, dtype=dtype, page_size=4, max_tokens=192, max_slots=3, max_positions=96, shuffle_seed=2)
+    # two groups of pages: the windowed entries (0 and 2) and the full ones (3); a state slab for entry 1
+    assert len(engine.cache.groups) == 2 and sorted(len(g.entries) for g in engine.cache.groups) == [1, 2]
+    assert list(engine.cache.states) == [1]
+    g = torch.Generator().manual_seed(3)
+    seqs = {r: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for r, n in (("a", 41), ("b", 23))}
+    want = {r: toy_plain_forward(cfg, w, t) for r, t in seqs.items()}
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    rp = Replayer(engine)
+    fed = {"a": 0, "b": 0}
+
+    def entry(r, n):
+        t = seqs[r][fed[r]:fed[r] + n]
+        e = {"id": r, "tokens": t, "want": list(range(len(t)))}
+        fed[r] += len(t)
+        return e
+    plan = [[("a", 9)], [("a", 1), ("b", 5)], [("a", 2), ("b", 1)], [("b", 17)], [("a", 29)]]
+    for k, row in enumerate(plan):
+        ents, rows = [], []
+        for r, n in row:
+            start = fed[r]
+            e = entry(r, n)
+            ents.append(e)
+            rows += [want[r][start + j] for j in range(len(e["tokens"]))]
+        got = rp.run_step({"step": k, "entries": ents, "end": [r for r, _ in row if fed[r] == len(seqs[r])]})
+        close(got, torch.stack(rows), tol, f"toy architecture, step {k}")
+    # the windowed group gave pages back while "a" was still running; everything is free at the end
+    engine.cache.flush()
+    engine.cache.manager.check()
+    for gi in range(len(engine.cache.groups)):
+        assert engine.cache.manager.free_pages(gi) == engine.cache.n_pages
+    # a second request in the same slot starts from zeroed state
+    got = rp.run_step({"step": 9, "entries": [{"id": "c", "tokens": seqs["b"][:7], "want": [6]}], "end": ["c"]})
+    close(got, want["b"][6:7], tol, "state is zeroed for a new request")
