@@ -247,6 +247,17 @@ class Backend:
         return int(best.item())
 
     # -- many sequences -----------------------------------------------------
+    def decode_batch(self, tokens: Sequence[int], caches: Sequence[BackendCache]) -> List[int]:
+        """One decode step for several sequences at once: ``tokens[i]`` goes to the next
+        position of ``caches[i]``; the greedy picks, chosen on the device, come back as
+        host integers (the batch form of ``forward_argmax``)."""
+        if len(tokens) != len(caches):
+            raise StepError("decode_batch needs one token per cache")
+        logits = self.engine.step([StepEntry(c.slot, [int(t)], [0]) for c, t in zip(caches, tokens)])
+        best = torch.empty(len(caches), dtype=torch.int32, device=logits.device)
+        ops.argmax(logits, best)
+        return best.tolist()
+
     def generate_batch(self, prompts: Sequence[Sequence[int]], n_gen: Union[int, Sequence[int]],
                        stop: Sequence[int] = (), sample: Union[None, SampleCfg, Sequence[Optional[SampleCfg]]] = None,
                        on_token: Optional[Callable[[int, int], None]] = None,

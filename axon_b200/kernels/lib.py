@@ -122,7 +122,18 @@ class KernelError(RuntimeError):
     """A launcher refused its arguments or the launch failed."""
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers of the library have been called so far (each launches
+    its kernels on the current stream; benches report the difference over a region)."""
+    return _launches
+
+
 def check(status: int) -> None:
+    global _launches
+    _launches += 1
     if status != 0:
         msg = cuda().axon_last_error().decode("utf-8", "replace")
         raise KernelError(msg or f"kernel launcher returned {status}")
