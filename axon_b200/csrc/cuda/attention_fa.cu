@@ -1,0 +1,400 @@
+// Causal grouped-query attention over the paged cache on the tensor cores
+// (bfloat16 in, float accumulation, softmax in float).
+//
+// One kernel, two shapes of work:
+//
+//  * prefill: a CTA owns up to 64 query rows of one (request, kv head): rows are
+//    (token, head of the group) pairs, token-major, so all heads of a group share the
+//    keys they read.  Its 4 warps own 16 rows each and sweep 64-key tiles.
+//  * decode: a CTA owns up to 16 query rows (one token's group of heads, or a few
+//    tokens') and a contiguous share ("split") of the key tiles; inside a tile each
+//    warp takes 16 of the 64 keys and the warps merge at the end.  With more than one
+//    split the CTA writes an unnormalised partial (o, m, l) to scratch and a second
+//    kernel folds the splits in ascending order.
+//
+// Keys and values are gathered row by row through the block table (any page size)
+// with 16-byte cp.async into a swizzled shared tile, double-buffered.  A row of a
+// tile is one key of one kv head (head_dim elements, contiguous in its page).
+// Scores are masked per element: key <= query position, and key > position - window
+// when a window is set, so the result does not depend on how the tokens were cut
+// into steps or tiles.
+#include "common.cuh"
+
+namespace axon {
+
+constexpr int FA_BN = 64;       // keys per tile
+constexpr int FA_THREADS = 128; // 4 warps
+
+struct FaParams {
+    const __nv_bfloat16* q;      // [tokens][heads * hd]
+    const __nv_bfloat16* pool;
+    __nv_bfloat16* out;          // [tokens][heads * hd]
+    const int32_t* segments;     // [4][n_segments]: slot, q_start, q_len, kv_len
+    const int32_t* items;        // [n_items][2]: segment, first token of the tile within the segment
+    float* part_o;               // [items][kv_heads][splits][16][hd]   (decode, splits > 1)
+    float* part_ml;              // [items][kv_heads][splits][16][2]
+    PagedKv kv;
+    int n_segments, heads, group, tokens_per_tile, n_splits, window;
+    float scale_log2;            // scale * log2(e)
+};
+
+template <int HD> struct Swz {
+    static constexpr int CPR = HD / 8;  // 16-byte chunks per row
+    static __device__ __forceinline__ int chunk(int row, int c) {
+        if (CPR >= 8) return c ^ (row & 7);
+        constexpr int RP = CPR >= 8 ? 1 : 8 / CPR;  // rows per 128 bytes
+        return c ^ ((row / RP) % CPR);
+    }
+    // byte offset of chunk c of row r in a tile
+    static __device__ __forceinline__ uint32_t off(int row, int c) { return (uint32_t)(row * CPR + chunk(row, c)) * 16u; }
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather one 64-key tile of K or V (plane_off selects) for kv head `kvh` into shared memory.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(uint32_t smem_tile, const __nv_bfloat16* pool, const PagedKv& kv,
+                                             int slot, int kvh, int key0, int kv_len, long long plane_off) {
+    constexpr int CPR = HD / 8;
+    for (int e = threadIdx.x; e < FA_BN * CPR; e += FA_THREADS) {
+        const int r = e / CPR, c = e % CPR;
+        int pos = key0 + r;
+        // rows past the request's length read its last position: finite data, masked later
+        if (pos >= kv_len) pos = kv_len - 1;
+        const __nv_bfloat16* src = pool + kv.row(slot, pos, kvh) + plane_off + c * 8;
+        cp_async16(smem_tile + Swz<HD>::off(r, c), src);
+    }
+}
+
+template <int HD, bool DECODE>
+__global__ void __launch_bounds__(FA_THREADS)
+attention_fa_kernel(const FaParams p) {
+    constexpr int BM = DECODE ? 16 : 64;
+    constexpr int CPR = HD / 8;
+    constexpr int KSTEPS = HD / 16;           // k-steps of Q.K^T
+    constexpr int NT_S = DECODE ? 2 : 8;      // 8-key score tiles per warp
+    constexpr int NT_O = HD / 8;              // 8-dim output tiles
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t q_sm = smem;
+    const uint32_t k_sm = q_sm + BM * HD * 2;
+    const uint32_t v_sm = k_sm + 2 * FA_BN * HD * 2;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
+    const int slot = p.segments[seg], q_start = p.segments[p.n_segments + seg];
+    const int q_len = p.segments[2 * p.n_segments + seg], kv_len = p.segments[3 * p.n_segments + seg];
+    const int ntok = min(p.tokens_per_tile, q_len - tok0);
+    const int rows_used = ntok * p.group;
+    const int pos0 = kv_len - q_len + tok0;           // position of the tile's first token
+    const int kv_hi = pos0 + ntok;                    // keys [kv_lo, kv_hi) matter to this tile
+    const int kv_lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    const int tile_lo = kv_lo / FA_BN, tile_hi = (kv_hi + FA_BN - 1) / FA_BN;
+    const int per = (tile_hi - tile_lo + p.n_splits - 1) / p.n_splits;
+    const int t_begin = tile_lo + split * per, t_end = min(tile_hi, t_begin + per);
+
+    // ---- Q tile -> shared (rows beyond rows_used are zero)
+    for (int e = threadIdx.x; e < BM * CPR; e += FA_THREADS) {
+        const int r = e / CPR, c = e % CPR;
+        const uint32_t dst = q_sm + Swz<HD>::off(r, c);
+        if (r < rows_used) {
+            const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+            cp_async16(dst, p.q + ((long long)tok * p.heads + head) * HD + c * 8);
+        } else {
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u));
+        }
+    }
+    if (t_begin < t_end) {
+        load_kv_tile<HD>(k_sm, p.pool, p.kv, slot, kvh, t_begin * FA_BN, kv_len, 0);
+        load_kv_tile<HD>(v_sm, p.pool, p.kv, slot, kvh, t_begin * FA_BN, kv_len, p.kv.v_offset);
+    }
+    cp_async_commit();
+
+    // rows this thread holds: r_a = base + g, r_b = base + g + 8
+    const int row_base = DECODE ? 0 : warp * 16;
+    const int ra = row_base + g, rb = ra + 8;
+    const int pos_a = pos0 + ra / p.group, pos_b = pos0 + rb / p.group;   // query positions
+    const int lo_a = (p.window > 0) ? pos_a - p.window + 1 : 0, lo_b = (p.window > 0) ? pos_b - p.window + 1 : 0;
+
+    uint32_t qf[KSTEPS][4];
+    float o[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    for (int tile = t_begin; tile < t_end; ++tile) {
+        const int buf = (tile - t_begin) & 1;
+        cp_async_wait_all();
+        __syncthreads();
+        if (tile + 1 < t_end) {
+            load_kv_tile<HD>(k_sm + (buf ^ 1) * FA_BN * HD * 2, p.pool, p.kv, slot, kvh, (tile + 1) * FA_BN, kv_len, 0);
+            load_kv_tile<HD>(v_sm + (buf ^ 1) * FA_BN * HD * 2, p.pool, p.kv, slot, kvh, (tile + 1) * FA_BN, kv_len, p.kv.v_offset);
+        }
+        cp_async_commit();
+        if (tile == t_begin) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const int r = row_base + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
+                ldsm_x4(q_sm + Swz<HD>::off(r, c), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+            }
+        }
+        const uint32_t kt = k_sm + buf * FA_BN * HD * 2, vt = v_sm + buf * FA_BN * HD * 2;
+        const int key_base = DECODE ? warp * 16 : 0;   // first key (within the tile) of this warp
+
+        // ---- S = Q K^T
+        float s[NT_S][4];
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int jp = 0; jp < NT_S / 2; ++jp) {
+                const int n = key_base + jp * 16 + (lane & 7) + ((lane >> 4) & 1) * 8, c = 2 * ks + ((lane >> 3) & 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(kt + Swz<HD>::off(n, c), b0, b1, b2, b3);
+                mma16816(s[2 * jp], qf[ks], b0, b1);
+                mma16816(s[2 * jp + 1], qf[ks], b2, b3);
+            }
+        }
+        // ---- mask, scale, online softmax
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+            const int key = tile * FA_BN + key_base + j * 8 + 2 * t;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int kp = key + i;
+                const bool ok_a = kp <= pos_a && kp >= lo_a, ok_b = kp <= pos_b && kp >= lo_b;
+                s[j][i] = ok_a ? s[j][i] * p.scale_log2 : -INFINITY;
+                s[j][2 + i] = ok_b ? s[j][2 + i] * p.scale_log2 : -INFINITY;
+                mx_a = fmaxf(mx_a, s[j][i]);
+                mx_b = fmaxf(mx_b, s[j][2 + i]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float use_a = (mn_a == -INFINITY) ? 0.f : mn_a, use_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);   // exp2(-inf) = 0 on the first tile
+        m_a = mn_a; m_b = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+        uint32_t pf[NT_S / 2][4];
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+            const float p0 = exp2f(s[j][0] - use_a), p1 = exp2f(s[j][1] - use_a);
+            const float p2 = exp2f(s[j][2] - use_b), p3 = exp2f(s[j][3] - use_b);
+            sum_a += p0 + p1; sum_b += p2 + p3;
+            pf[j / 2][(j & 1) * 2] = pack_bf16(p0, p1);
+            pf[j / 2][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_a = l_a * corr_a + sum_a;
+        l_b = l_b * corr_b + sum_b;
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) { o[j][0] *= corr_a; o[j][1] *= corr_a; o[j][2] *= corr_b; o[j][3] *= corr_b; }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < NT_S / 2; ++kk) {
+#pragma unroll
+            for (int jp = 0; jp < NT_O / 2; ++jp) {
+                const int krow = key_base + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * jp + (lane >> 4);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(vt + Swz<HD>::off(krow, c), b0, b1, b2, b3);
+                mma16816(o[2 * jp], pf[kk], b0, b1);
+                mma16816(o[2 * jp + 1], pf[kk], b2, b3);
+            }
+        }
+    }
+    // the row sums live spread over the quad
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    if (!DECODE) {
+        // every warp owns its rows: normalise and store
+        const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? rb : ra;
+            if (r >= rows_used) continue;
+            const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+            __nv_bfloat16* dst = p.out + ((long long)tok * p.heads + head) * HD;
+            const float inv = half ? inv_b : inv_a;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                const uint32_t v = pack_bf16(o[j][2 * half] * inv, o[j][2 * half + 1] * inv);
+                *reinterpret_cast<uint32_t*>(dst + j * 8 + 2 * t) = v;
+            }
+        }
+        return;
+    }
+
+    // ---- decode: merge the 4 warps (each saw a quarter of every tile's keys)
+    cp_async_wait_all();
+    __syncthreads();
+    float* mo = reinterpret_cast<float*>(smem_raw + BM * HD * 2);   // [4][16][HD] over the K/V tiles
+    float* mml = mo + 4 * 16 * HD;                                   // [4][16][2]
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+        float* a = mo + ((warp * 16 + g) * HD) + j * 8 + 2 * t;
+        float* b = mo + ((warp * 16 + g + 8) * HD) + j * 8 + 2 * t;
+        a[0] = o[j][0]; a[1] = o[j][1]; b[0] = o[j][2]; b[1] = o[j][3];
+    }
+    if (t == 0) {
+        mml[(warp * 16 + g) * 2] = m_a; mml[(warp * 16 + g) * 2 + 1] = l_a;
+        mml[(warp * 16 + g + 8) * 2] = m_b; mml[(warp * 16 + g + 8) * 2 + 1] = l_b;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * HD; e += FA_THREADS) {
+        const int r = e / HD, d = e % HD;
+        if (r >= rows_used) continue;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
+        const float use = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(mml[(w * 16 + r) * 2] - use);
+            l += mml[(w * 16 + r) * 2 + 1] * f;
+            acc += mo[(w * 16 + r) * HD + d] * f;
+        }
+        if (p.n_splits == 1) {
+            const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+            p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const long long base = (((long long)item * gridDim.y + kvh) * p.n_splits + split) * 16 + r;
+            p.part_o[base * HD + d] = acc;
+            if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
+        }
+    }
+}
+
+// Fold the splits of each (item, kv head, row) in ascending order and normalise.
+template <int HD>
+__global__ void attention_combine_kernel(const FaParams p) {
+    const int item = blockIdx.x, kvh = blockIdx.y;
+    const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
+    const int q_start = p.segments[p.n_segments + seg], q_len = p.segments[2 * p.n_segments + seg];
+    const int rows_used = min(p.tokens_per_tile, q_len - tok0) * p.group;
+    for (int e = threadIdx.x; e < rows_used * HD; e += blockDim.x) {
+        const int r = e / HD, d = e % HD;
+        const long long base = ((long long)item * gridDim.y + kvh) * p.n_splits * 16 + r;
+        float m = -INFINITY;
+        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, p.part_ml[(base + (long long)s * 16) * 2]);
+        const float use = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+        for (int s = 0; s < p.n_splits; ++s) {
+            const long long b = base + (long long)s * 16;
+            const float f = exp2f(p.part_ml[b * 2] - use);
+            l += p.part_ml[b * 2 + 1] * f;
+            acc += p.part_o[b * HD + d] * f;
+        }
+        const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+        p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+}
+
+template <int HD, bool DECODE>
+static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t stream) {
+    constexpr int BM = DECODE ? 16 : 64;
+    constexpr size_t tiles = (size_t)BM * HD * 2 + 4 * (size_t)FA_BN * HD * 2;
+    constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
+    constexpr size_t smem = tiles > merge ? tiles : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_fa_kernel<HD, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_error("axon_attention_fa: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; }
+        configured = true;
+    }
+    dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);
+    attention_fa_kernel<HD, DECODE><<<grid, FA_THREADS, smem, stream>>>(p);
+    int st = launch_status("axon_attention_fa");
+    if (st != AXON_OK) return st;
+    if (DECODE && p.n_splits > 1) {
+        attention_combine_kernel<HD><<<dim3(n_items, kv_heads), 128, 0, stream>>>(p);
+        st = launch_status("axon_attention_fa combine");
+    }
+    return st;
+}
+
+}  // namespace axon
+
+using namespace axon;
+
+struct AxonKvLayoutFa {
+    const int32_t* block_table;
+    int32_t table_stride, page_size, kv_heads, head_dim;
+    int64_t page_stride, entry_offset, v_offset;
+};
+
+// How many floats of scratch a decode launch with these sizes needs (0 when splits == 1).
+AXON_API long long axon_attention_fa_scratch_floats(int n_items, int kv_heads, int n_splits, int head_dim) {
+    if (n_splits <= 1) return 0;
+    return (long long)n_items * kv_heads * n_splits * 16 * (head_dim + 2);
+}
+
+// decode != 0: tiles of 16 rows with `n_splits` key shares; else tiles of 64 rows.
+// tokens_per_tile * group rows must fit the tile.  scratch: see above (may be null when
+// n_splits == 1).  Head sizes 16, 32, 64, 128; group <= 16 (decode) or 64 (prefill).
+AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
+                               const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
+                               float scale, int window, int decode, int tokens_per_tile, int n_splits,
+                               float* scratch, cudaStream_t stream) {
+    if (n_items <= 0) return AXON_OK;
+    const int hd = layout->head_dim, kvh = layout->kv_heads;
+    if (heads % kvh) { set_error("axon_attention_fa: %d heads over %d kv heads", heads, kvh); return AXON_BAD_ARGUMENT; }
+    const int group = heads / kvh, bm = decode ? 16 : 64;
+    if (tokens_per_tile < 1 || tokens_per_tile * group > bm) { set_error("axon_attention_fa: %d tokens x %d heads do not fit a tile of %d rows", tokens_per_tile, group, bm); return AXON_BAD_ARGUMENT; }
+    if (n_splits < 1 || (!decode && n_splits != 1)) { set_error("axon_attention_fa: bad split count %d", n_splits); return AXON_BAD_ARGUMENT; }
+    if (n_splits > 1 && scratch == nullptr) { set_error("axon_attention_fa: splits need scratch memory"); return AXON_BAD_ARGUMENT; }
+    if (((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) { set_error("axon_attention_fa: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
+    FaParams p;
+    p.q = (const __nv_bfloat16*)q; p.pool = (const __nv_bfloat16*)pool; p.out = (__nv_bfloat16*)out;
+    p.segments = segments; p.items = items;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (long long)n_items * kvh * n_splits * 16 * hd : nullptr;
+    p.kv.block_table = layout->block_table; p.kv.table_stride = layout->table_stride; p.kv.page_size = layout->page_size;
+    p.kv.kv_heads = kvh; p.kv.head_dim = hd; p.kv.page_stride = layout->page_stride;
+    p.kv.entry_offset = layout->entry_offset; p.kv.v_offset = layout->v_offset;
+    p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile;
+    p.n_splits = n_splits; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+#define AXON_FA_CASE(HD)                                                                         \
+    case HD: return decode ? launch_fa<HD, true>(p, n_items, kvh, stream) : launch_fa<HD, false>(p, n_items, kvh, stream);
+    switch (hd) {
+        AXON_FA_CASE(16)
+        AXON_FA_CASE(32)
+        AXON_FA_CASE(64)
+        AXON_FA_CASE(128)
+        default: set_error("axon_attention_fa: head size %d is not 16, 32, 64 or 128", hd); return AXON_BAD_ARGUMENT;
+    }
+#undef AXON_FA_CASE
+}

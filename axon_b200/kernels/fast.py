@@ -1,7 +1,8 @@
 """The tuned sm_100a kernels of the bfloat16 path.
 
 Each function returns True when it ran and False when it refuses the sizes or
-dtypes, in which case the caller takes the plain kernel.
+dtypes, in which case the caller takes the plain kernel.  What each kernel needs is
+checked here, before the launch, so a refusal never costs a failed launch.
 """
 
 from __future__ import annotations
@@ -10,15 +11,117 @@ from typing import Optional
 
 import torch
 
+from . import lib
+from .lib import check
+
+EPI_STORE_F32, EPI_STORE_BF16, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+SMALL_M = 64
+
+#: switches for tests that compare a tuned kernel with the plain one
+ENABLED = {"gemm_small_m": True, "gemm_tc": True, "attention_prefill": True, "attention_decode": True}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _bf16_operands(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+            and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor],
          accumulate: bool) -> bool:
+    if not _bf16_operands(a, w):
+        return False
+    M, K = a.shape
+    N = w.shape[0]
+    if accumulate:
+        if out.dtype != torch.float32:
+            return False
+        epi = EPI_RESIDUAL
+    elif out.dtype == torch.float32:
+        epi = EPI_STORE_F32
+    elif out.dtype == torch.bfloat16:
+        epi = EPI_STORE_BF16
+    else:
+        return False
+    if M <= SMALL_M and ENABLED["gemm_small_m"]:
+        check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
+                                           out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
+        return True
     return False
 
 
 def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
+    if not _bf16_operands(h, w_gate_up) or act.dtype != torch.bfloat16:
+        return False
+    M, K = h.shape
+    N = w_gate_up.shape[0]
+    if M <= SMALL_M and ENABLED["gemm_small_m"]:
+        check(lib.cuda().axon_gemm_small_m(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,
+                                           M, N, K, K, act.stride(0), _stream()))
+        return True
     return False
+
+
+FA_HEAD_DIMS = (16, 32, 64, 128)
+SM_COUNT = 148
+
+
+def _attention_items(ctx, group: int):
+    """Work lists for the step's segments, cached per step and group size: segments that
+    fit a 16-row tile (one or two decoded tokens) go to the decode shape, the others are
+    cut into tiles of up to 64 rows."""
+    key = ("fa_items", group)
+    got = ctx.scratch.get(key)
+    if got is not None:
+        return got
+    tpt_dec, tpt_pre = (16 // group if group <= 16 else 0), 64 // group
+    dec, pre = [], []
+    dec_kv = 0
+    for s, (n, kv_len) in enumerate(zip(ctx.seg_q_len, ctx.seg_kv_len)):
+        if tpt_dec and n <= tpt_dec:
+            dec += [s, 0]
+            dec_kv = max(dec_kv, kv_len)
+        else:
+            for t0 in range(0, n, tpt_pre):
+                pre += [s, t0]
+    dev = ctx.tokens.device
+    both = torch.tensor(dec + pre, dtype=torch.int32, device=dev) if dec or pre else None
+    got = {"dec": both[:len(dec)] if dec else None, "n_dec": len(dec) // 2, "dec_kv": dec_kv,
+           "pre": both[len(dec):] if pre else None, "n_pre": len(pre) // 2,
+           "tpt_dec": tpt_dec, "tpt_pre": tpt_pre}
+    ctx.scratch[key] = got
+    return got
 
 
 def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
-    return False
+    """Tensor-core attention over the paged cache; refuses head sizes other than
+    16/32/64/128, groups of more than 64 heads, and dtypes other than bfloat16."""
+    if not (ENABLED["attention_prefill"] and ENABLED["attention_decode"]):
+        return False
+    if q.dtype != torch.bfloat16 or kv.pool.dtype != torch.bfloat16 or kv.head_dim not in FA_HEAD_DIMS:
+        return False
+    if heads % kv.kv_heads or heads // kv.kv_heads > 64 or ctx.segments is None:
+        return False
+    group = heads // kv.kv_heads
+    it = _attention_items(ctx, group)
+    cu = lib.cuda()
+    n_seg = len(ctx.seg_slot)
+    if it["n_dec"]:
+        tiles = -(-it["dec_kv"] // 64)
+        splits = max(1, min(tiles, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads))))
+        scratch = None
+        if splits > 1:
+            scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * splits * 16 * (kv.head_dim + 2),),
+                                    torch.float32)
+        check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
+                                   it["dec"].data_ptr(), it["n_dec"], kv._ref, heads, float(scale), int(kv.window),
+                                   1, it["tpt_dec"], splits, None if scratch is None else scratch.data_ptr(),
+                                   _stream()))
+    if it["n_pre"]:
+        check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
+                                   it["pre"].data_ptr(), it["n_pre"], kv._ref, heads, float(scale), int(kv.window),
+                                   0, it["tpt_pre"], 1, None, _stream()))
+    return True

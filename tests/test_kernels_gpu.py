@@ -310,3 +310,120 @@ def test_residual_add_and_convert(ops, dtype):
     out = torch.empty(7, 33, dtype=dtype, device=DEV)
     ops.convert(x, out)
     assert torch.equal(out, x.to(dtype))
+
+
+# ---------------------------------------------------------------------------
+# the tuned bfloat16 kernels, each against float64
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 23, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(16, 64), (2, 8), (33, 24), (1000, 160), (344, 344), (130, 1096), (4608, 3584)])
+def test_gemm_small_m(ops, M, N, K):
+    from axon_b200.kernels import fast
+    a = rand(M, K, dtype=torch.bfloat16, seed=70)
+    w = rand(N, K, dtype=torch.bfloat16, seed=71, std=0.1)
+    bias = rand(N, seed=72)
+    want = a.double() @ w.double().T
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    assert fast.gemm(a, w, out, None, False)
+    close(out, want, 2e-5, f"small-M product {M}x{N}x{K}")
+    assert fast.gemm(a, w, out, bias, False)
+    close(out, want + bias.double(), 2e-5, "with bias")
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert fast.gemm(a, w, outb, bias, False)
+    close(outb, want + bias.double(), OUT_TOL[torch.bfloat16], "bfloat16 output")
+    res = rand(M, N, seed=73)
+    acc = res.clone()
+    assert fast.gemm(a, w, acc, None, True)
+    close(acc, want + res.double(), 2e-5, "into the residual")
+    if N % 2 == 0:
+        act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        assert fast.gemm_swiglu(a, w, act)
+        g, u = want[:, 0::2], want[:, 1::2]
+        close(act, g / (1 + torch.exp(-g)) * u, OUT_TOL[torch.bfloat16], "SwiGLU epilogue")
+
+
+def test_gemm_small_m_refusals(ops):
+    from axon_b200.kernels import fast
+    a, w = rand(4, 12, dtype=torch.bfloat16), rand(5, 12, dtype=torch.bfloat16)
+    out = torch.empty(4, 5, dtype=torch.float32, device=DEV)
+    assert not fast.gemm(a, w, out, None, False)            # K % 8 != 0: the caller takes the plain kernel
+    assert not fast.gemm(a.float(), w.float(), out, None, False)
+    from axon_b200.kernels import linear
+    linear.linear(a, w, out)                                 # and gets the right result there
+    close(out, a.double() @ w.double().T, 2e-5)
+
+
+def _ctx_for(segs):
+    """A StepContext for segments [(slot, q_len, kv_len)] with tokens flattened in order."""
+    from axon_b200.parts import Runtime, StepContext
+    rt = Runtime(torch.bfloat16, DEV)
+    pos, slot_of, rows, at = [], [], [[], [], [], []], 0
+    for slot, n, kv_len in segs:
+        pos += list(range(kv_len - n, kv_len))
+        slot_of += [slot] * n
+        for lst, v in zip(rows, (slot, at, n, kv_len)):
+            lst.append(v)
+        at += n
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return StepContext(rt=rt, n_tokens=at, tokens=i32([0] * at), positions=i32(pos), token_slot=i32(slot_of),
+                       seg_slot=rows[0], seg_q_start=rows[1], seg_q_len=rows[2], seg_kv_len=rows[3],
+                       segments=i32(rows), host_positions=pos)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,ps,window", [
+    (4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (6, 2, 64, 8, 0), (28, 4, 128, 16, 0), (8, 8, 128, 16, 0),
+    (40, 2, 64, 16, 0), (7, 1, 128, 1, 0), (6, 2, 64, 16, 70), (4, 2, 128, 16, 9)])
+def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window):
+    """The tensor-core kernel on a mixed batch: decoded tokens at short and long contexts
+    (one key; several splits), two-token portions, a whole prompt, a portion in the middle
+    of a long request.  One key far back gets a large score so that a wrong page or a
+    dropped tile shows."""
+    from axon_b200.kernels import fast
+    # (q_len, kv_len) per request
+    shapes = [(1, 1), (1, 700), (2, 131), (100, 100), (37, 300), (1, 64), (1, 65), (3, 3)]
+    max_pos = 704
+    slots = len(shapes)
+    view, table = make_cache(ops, torch.bfloat16, kv_heads, hd, ps, slots * -(-max_pos // ps), slots, max_pos,
+                             window=window, seed=13)
+    group = heads // kv_heads
+    ks, vs = [], []
+    for s, (n, kv_len) in enumerate(shapes):
+        k = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=200 + s)
+        v = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=300 + s)
+        ks.append(k); vs.append(v)
+        for pos in range(kv_len):
+            page = int(table[s, pos // ps])
+            view.pool[page, view.entry, 0, :, pos % ps, :] = k[pos]
+            view.pool[page, view.entry, 1, :, pos % ps, :] = v[pos]
+    ctx = _ctx_for([(s, n, kv_len) for s, (n, kv_len) in enumerate(shapes)])
+    q = rand(ctx.n_tokens, heads * hd, dtype=torch.bfloat16, seed=400)
+    # the last query of request 1 lines up with its key 17 (far back) on every head
+    qv = q.view(ctx.n_tokens, heads, hd)
+    for h in range(heads):
+        qv[1, h] = (ks[1][17, h // group].float() * 1.5).to(torch.bfloat16)
+    out = torch.zeros_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    assert fast.attention(q, view, ctx, out, heads, scale)
+    plain_out = torch.zeros_like(q)
+    ops.attention_plain(q, view, ctx.positions, ctx.token_slot, plain_out, heads, scale)
+    at = 0
+    for s, (n, kv_len) in enumerate(shapes):
+        for i in range(n):
+            pos = kv_len - n + i
+            lo = max(0, pos - window + 1) if window else 0
+            for h in range(heads):
+                qh = q[at + i].view(heads, hd)[h].double()
+                kk, vv = ks[s][lo:pos + 1, h // group].double(), vs[s][lo:pos + 1, h // group].double()
+                w = torch.softmax((kk @ qh) * scale, dim=0)
+                want = w @ vv
+                close(out[at + i].view(heads, hd)[h], want, 1.5e-2, f"request {s} token {i} head {h}")
+                close(plain_out[at + i].view(heads, hd)[h], want, 1e-2, f"plain kernel, request {s} token {i} head {h}")
+        at += n
+
+
+def test_attention_tensor_core_refusals(ops):
+    from axon_b200.kernels import fast
+    view, _ = make_cache(ops, torch.bfloat16, 1, 48, 16, 4, 1, 64)
+    ctx = _ctx_for([(0, 1, 5)])
+    q = rand(1, 2 * 48, dtype=torch.bfloat16)
+    assert not fast.attention(q, view, ctx, torch.empty_like(q), 2, 0.1)       # head size 48: the plain kernel runs
