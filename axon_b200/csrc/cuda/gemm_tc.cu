@@ -1,0 +1,344 @@
+// bfloat16 products on the 5th-generation tensor cores: out[m][n] = sum_k a[m][k] w[n][k].
+//
+// One CTA computes a 128 x BN tile of the output (BN = 256 or 128).  Operands are both
+// K-major, so activations [M][K] and weights [N][K] are loaded as they lie in memory:
+// a TMA producer thread copies 128 x 64 and BN x 64 element boxes (128-byte swizzle)
+// into a ring of shared-memory stages; one MMA thread issues tcgen05.mma (M 128, N BN,
+// K 16) four times per stage into a float accumulator in tensor memory and releases the
+// stage with tcgen05.commit; four epilogue warps read the accumulator back with
+// tcgen05.ld (a thread per output row) and apply the epilogue: store as float or
+// bfloat16 with an optional bias, add into a float residual, or SwiGLU over interleaved
+// gate/up columns.  Tails in M, N and K are zero-filled by TMA and masked at the store.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up, the kernel records it in a
+// device flag (read with axon_gemm_tc_status) and carries on to its end, so tensor
+// memory is always freed and nothing spins forever.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+namespace axon {
+
+constexpr int TC_BM = 128, TC_BK = 64, TC_UMMA_K = 16;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;   // polls of try_wait before a wait gives up
+
+__device__ unsigned int g_tc_error = 0;        // 0 fine; else 1 + the role that gave up
+
+// ---- mbarrier / TMA / tcgen05 wrappers ------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Wait until the phase with this parity completes, at most TC_WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t role) {
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicMax(&g_tc_error, 1u + role);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t smem, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile with 128-byte rows, 128-byte swizzle;
+// 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with a swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+enum { TC_STORE_F32 = 0, TC_STORE_BF16 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3 };
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int ldo, int m_tiles) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    extern __shared__ unsigned char smem_dyn[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(&bars[0]);
+    const uint32_t empty0 = full0 + 8 * STAGES, tmem_full = full0 + 16 * STAGES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tile = blockIdx.x % m_tiles, n_tile = blockIdx.x / m_tiles;
+    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
+    const int k_stages = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // this warp owns tensor memory: BN float columns for the accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            for (int ks = 0; ks < k_stages; ++ks) {
+                const int s = ks % STAGES;
+                if (ks >= STAGES) mbar_wait(empty0 + 8 * s, ((ks / STAGES) - 1) & 1, 0);
+                const uint32_t sa = smem_base + s * STAGE_BYTES, sw = sa + A_BYTES;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(sa, &map_a, ks * TC_BK, m0, full0 + 8 * s);
+                tma_load_2d(sw, &map_w, ks * TC_BK, n0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(TC_BM, BN);
+            for (int ks = 0; ks < k_stages; ++ks) {
+                const int s = ks % STAGES;
+                mbar_wait(full0 + 8 * s, (ks / STAGES) & 1, 1);
+                tc_fence_after();
+                const uint32_t sa = smem_base + s * STAGE_BYTES, sw = sa + A_BYTES;
+                const uint64_t da = smem_desc(sa), db = smem_desc(sw);
+#pragma unroll
+                for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+                    // 16 elements = 32 bytes along K inside the swizzled row: +2 in the address field
+                    umma(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (ks | k) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
+            }
+            umma_commit(tmem_full);               // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ..
+        mbar_wait(tmem_full, 0, 2);
+        tc_fence_after();
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
+            const int nc = n0 + c * 32;
+            if (m >= M || nc >= N) continue;
+            if (EPI == TC_SWIGLU) {
+                __nv_bfloat16* dst = (__nv_bfloat16*)out + (long long)m * ldo + (nc >> 1);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (nc + 2 * i + 1 < N) {
+                        float gv = __uint_as_float(r[2 * i]), uv = __uint_as_float(r[2 * i + 1]);
+                        if (bias) { gv += bias[nc + 2 * i]; uv += bias[nc + 2 * i + 1]; }
+                        dst[i] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                    }
+                }
+            } else if (EPI == TC_STORE_BF16) {
+                __nv_bfloat16* dst = (__nv_bfloat16*)out + (long long)m * ldo + nc;
+                const bool full = (nc + 32 <= N) && ((((uintptr_t)dst) & 15) == 0);
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float a = __uint_as_float(r[8 * i + 2 * j]), b = __uint_as_float(r[8 * i + 2 * j + 1]);
+                            if (bias) { a += bias[nc + 8 * i + 2 * j]; b += bias[nc + 8 * i + 2 * j + 1]; }
+                            __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                            pk[j] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (nc + i < N) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]) + (bias ? bias[nc + i] : 0.f));
+                }
+            } else {
+                float* dst = (float*)out + (long long)m * ldo + nc;
+                const bool full = (nc + 32 <= N) && ((((uintptr_t)dst) & 15) == 0);
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                               __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                        if (bias) { v.x += bias[nc + 4 * i]; v.y += bias[nc + 4 * i + 1]; v.z += bias[nc + 4 * i + 2]; v.w += bias[nc + 4 * i + 3]; }
+                        if (EPI == TC_RESIDUAL) {
+                            const float4 o = *reinterpret_cast<const float4*>(dst + 4 * i);
+                            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                        }
+                        *reinterpret_cast<float4*>(dst + 4 * i) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (nc + i < N) {
+                            float v = __uint_as_float(r[i]) + (bias ? bias[nc + i] : 0.f);
+                            if (EPI == TC_RESIDUAL) v += dst[i];
+                            dst[i] = v;
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ---- host side: tensor maps ---------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
+    }
+};
+
+// A [rows][cols] bfloat16 row-major matrix seen as boxes of box_rows x 64 elements.
+static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{ptr, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("axon_gemm_tc: cuTensorMapEncodeTiled is not available from this driver"); return false; }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("axon_gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d cols %d)", (int)r, rows, cols); return false; }
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+template <int BN, int STAGES>
+static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M,
+                     int N, int K, int ldo, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const dim3 grid((unsigned)(m_tiles * n_tiles)), block(192);
+#define AXON_TC_LAUNCH(E)                                                                                          \
+    {                                                                                                              \
+        static bool configured = false;                                                                            \
+        if (!configured) {                                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) { set_error("axon_gemm_tc: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
+            configured = true;                                                                                     \
+        }                                                                                                          \
+        gemm_tc_kernel<BN, STAGES, E><<<grid, block, smem, stream>>>(ma, mw, bias, out, M, N, K, ldo, m_tiles);    \
+    }
+    switch (epi) {
+        case TC_STORE_F32: AXON_TC_LAUNCH(TC_STORE_F32) break;
+        case TC_STORE_BF16: AXON_TC_LAUNCH(TC_STORE_BF16) break;
+        case TC_RESIDUAL: AXON_TC_LAUNCH(TC_RESIDUAL) break;
+        case TC_SWIGLU: AXON_TC_LAUNCH(TC_SWIGLU) break;
+        default: set_error("axon_gemm_tc: unknown epilogue %d", epi); return AXON_BAD_ARGUMENT;
+    }
+#undef AXON_TC_LAUNCH
+    return launch_status("axon_gemm_tc");
+}
+
+}  // namespace axon
+
+using namespace axon;
+
+// a [M][K], w [N][K] bfloat16, contiguous, K % 8 == 0, 16-byte aligned.  Epilogues as in
+// axon_gemm_small_m: 0 float out, 1 bfloat16 out, 2 out += (float), 3 SwiGLU to bfloat16 [M][N/2].
+AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void* out, int epilogue, int M, int N,
+                          int K, int ldo, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return AXON_OK;
+    if (K <= 0 || K % 8) { set_error("axon_gemm_tc: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
+    if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
+    if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
+    const bool wide = N > 128;
+    CUtensorMap ma, mw;
+    if (!tensor_map(a, M, K, TC_BM, &ma) || !tensor_map(w, N, K, wide ? 256 : 128, &mw)) return AXON_BAD_ARGUMENT;
+    if (wide) return launch_tc<256, 4>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
+    return launch_tc<128, 6>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
+}
+
+// 0 when no kernel of this file ever gave up on a wait; else 1 + the role (0 producer,
+// 1 MMA, 2 epilogue).  Synchronises the device.
+AXON_API int axon_gemm_tc_status() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof v) != cudaSuccess) return -1;
+    return (int)v;
+}

@@ -50,7 +50,16 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                            out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
         return True
+    if ENABLED["gemm_tc"]:
+        check(lib.cuda().axon_gemm_tc(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
+                                      out.data_ptr(), epi, M, N, K, out.stride(0), _stream()))
+        return True
     return False
+
+
+def gemm_tc_status() -> int:
+    """0 when no tensor-core product ever gave up on a wait (synchronises the device)."""
+    return lib.cuda().axon_gemm_tc_status()
 
 
 def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
@@ -61,6 +70,10 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
     if M <= SMALL_M and ENABLED["gemm_small_m"]:
         check(lib.cuda().axon_gemm_small_m(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,
                                            M, N, K, K, act.stride(0), _stream()))
+        return True
+    if ENABLED["gemm_tc"]:
+        check(lib.cuda().axon_gemm_tc(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,
+                                      M, N, K, act.stride(0), _stream()))
         return True
     return False
 

@@ -53,6 +53,8 @@ _SIGNATURES = {
     "axon_topk": [P, P, P, P, c_int, c_int, c_longlong, P],
     "axon_sample_temperature": [P, P, P, P, c_int, c_int, c_longlong, P],
     "axon_gemm_small_m": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "axon_gemm_tc": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "axon_gemm_tc_status": [],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P],
 }

@@ -353,6 +353,40 @@ def test_gemm_small_m_refusals(ops):
     close(out, a.double() @ w.double().T, 2e-5)
 
 
+@pytest.mark.parametrize("M", [65, 128, 129, 300, 1100])
+@pytest.mark.parametrize("N,K", [(256, 64), (128, 8), (130, 72), (1000, 160), (344, 344), (2, 1096), (4608, 3584)])
+def test_gemm_tensor_core(ops, M, N, K):
+    """The tcgen05 kernel at sizes with tails in M, N and K, every epilogue."""
+    from axon_b200.kernels import fast
+    a = rand(M, K, dtype=torch.bfloat16, seed=80)
+    w = rand(N, K, dtype=torch.bfloat16, seed=81, std=0.1)
+    bias = rand(N, seed=82)
+    want = a.double() @ w.double().T
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    assert fast.gemm(a, w, out, None, False)
+    close(out, want, 2e-5, f"tensor-core product {M}x{N}x{K}")
+    assert fast.gemm(a, w, out, bias, False)
+    close(out, want + bias.double(), 2e-5, "with bias")
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert fast.gemm(a, w, outb, bias, False)
+    close(outb, want + bias.double(), OUT_TOL[torch.bfloat16], "bfloat16 output")
+    res = rand(M, N, seed=83)
+    acc = res.clone()
+    assert fast.gemm(a, w, acc, None, True)
+    close(acc, want + res.double(), 2e-5, "into the residual")
+    if N % 2 == 0:
+        act = torch.full((M, N // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+        assert fast.gemm_swiglu(a, w, act)
+        g, u = want[:, 0::2], want[:, 1::2]
+        close(act, g / (1 + torch.exp(-g)) * u, OUT_TOL[torch.bfloat16], "SwiGLU epilogue")
+    # a view into a larger buffer (rows of a workspace) is a valid operand too
+    big = torch.zeros(M + 3, K, dtype=torch.bfloat16, device=DEV)
+    big[3:] = a
+    assert fast.gemm(big[3:], w, out, None, False)
+    close(out, want, 2e-5, "operand at an offset")
+    assert fast.gemm_tc_status() == 0, "a wait inside the kernel gave up"
+
+
 def _ctx_for(segs):
     """A StepContext for segments [(slot, q_len, kv_len)] with tokens flattened in order."""
     from axon_b200.parts import Runtime, StepContext
