@@ -398,3 +398,49 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
     }
 #undef AXON_FA_CASE
 }
+
+// ---------------------------------------------------------------------------
+// The variant for callers that cannot allocate: see attention_fa_noalloc.h.
+#include "attention_fa_noalloc.h"
+
+// The split partials of one launch.  In host code this name is only a stand-in for
+// the symbol, not a device address: the address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_fa_noalloc_scratch[AXON_FA_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_fa_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device, once looked up
+}
+
+int axon_attention_fa_decode_noalloc(const void* q, const void* pool, void* out, const int32_t* segments,
+                                     int n_segments, const int32_t* items, int n_items,
+                                     const AxonKvLayoutFa* layout, int heads, float scale, int window,
+                                     int tokens_per_tile, int n_splits, cudaStream_t stream) {
+    if (n_items <= 0) return AXON_OK;
+    if (layout == nullptr || n_splits < 1) { set_error("axon_attention_fa_decode_noalloc: bad arguments"); return AXON_BAD_ARGUMENT; }
+    const long long need = (long long)n_items * layout->kv_heads * n_splits * 16 * (layout->head_dim + 2);
+    if (need > AXON_FA_NOALLOC_SCRATCH_FLOATS) {
+        set_error("axon_attention_fa_decode_noalloc: %d items x %d kv heads x %d splits need %lld floats of scratch; "
+                  "the built-in array holds %lld (use fewer splits, or axon_attention_fa with your own scratch)",
+                  n_items, layout->kv_heads, n_splits, need, (long long)AXON_FA_NOALLOC_SCRATCH_FLOATS);
+        return AXON_BAD_ARGUMENT;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("axon_attention_fa_decode_noalloc: cudaGetDevice: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+        return AXON_CUDA_ERROR;
+    }
+    if (g_fa_noalloc_ptr[dev] == nullptr) {
+        // set-up, once per device, with that device current
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_fa_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("axon_attention_fa_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return AXON_CUDA_ERROR;
+        }
+        g_fa_noalloc_ptr[dev] = ptr;
+    }
+    return axon_attention_fa(q, pool, out, segments, n_segments, items, n_items, layout, heads, scale, window,
+                             /*decode=*/1, tokens_per_tile, n_splits, g_fa_noalloc_ptr[dev], stream);
+}
