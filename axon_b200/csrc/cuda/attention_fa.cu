@@ -24,6 +24,7 @@ namespace axon {
 
 constexpr int FA_BN = 64;       // keys per tile
 constexpr int FA_THREADS = 128; // 4 warps
+constexpr int FA_MAX_SPLITS = 32;
 
 struct FaParams {
     const __nv_bfloat16* q;      // [tokens][heads * hd]
@@ -304,21 +305,34 @@ __global__ void attention_combine_kernel(const FaParams p) {
     const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
     const int q_start = p.segments[p.n_segments + seg], q_len = p.segments[2 * p.n_segments + seg];
     const int rows_used = min(p.tokens_per_tile, q_len - tok0) * p.group;
+    // weight of each split for each row: 2^(m_s - m) / l, via shared memory
+    __shared__ float wgt[FA_MAX_SPLITS][16];
+    const long long base0 = ((long long)item * gridDim.y + kvh) * p.n_splits * 16;
+    for (int e = threadIdx.x; e < p.n_splits * 16; e += blockDim.x)
+        wgt[e / 16][e % 16] = p.part_ml[(base0 + e) * 2];          // m_s of (split, row)
+    __syncthreads();
+    if (threadIdx.x < rows_used) {
+        const int r = threadIdx.x;
+        float m = -INFINITY;
+        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, wgt[s][r]);
+        const float use = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f;
+        for (int s = 0; s < p.n_splits; ++s) {
+            const float f = exp2f(wgt[s][r] - use);
+            l += p.part_ml[(base0 + s * 16 + r) * 2 + 1] * f;
+            wgt[s][r] = f;
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        for (int s = 0; s < p.n_splits; ++s) wgt[s][r] *= inv;
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < rows_used * HD; e += blockDim.x) {
         const int r = e / HD, d = e % HD;
-        const long long base = ((long long)item * gridDim.y + kvh) * p.n_splits * 16 + r;
-        float m = -INFINITY;
-        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, p.part_ml[(base + (long long)s * 16) * 2]);
-        const float use = (m == -INFINITY) ? 0.f : m;
-        float l = 0.f, acc = 0.f;
-        for (int s = 0; s < p.n_splits; ++s) {
-            const long long b = base + (long long)s * 16;
-            const float f = exp2f(p.part_ml[b * 2] - use);
-            l += p.part_ml[b * 2 + 1] * f;
-            acc += p.part_o[b * HD + d] * f;
-        }
+        float acc = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < p.n_splits; ++s) acc += p.part_o[(base0 + s * 16 + r) * HD + d] * wgt[s][r];
         const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
-        p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -373,7 +387,7 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
     if (heads % kvh) { set_error("axon_attention_fa: %d heads over %d kv heads", heads, kvh); return AXON_BAD_ARGUMENT; }
     const int group = heads / kvh, bm = decode ? 16 : 64;
     if (tokens_per_tile < 1 || tokens_per_tile * group > bm) { set_error("axon_attention_fa: %d tokens x %d heads do not fit a tile of %d rows", tokens_per_tile, group, bm); return AXON_BAD_ARGUMENT; }
-    if (n_splits < 1 || (!decode && n_splits != 1)) { set_error("axon_attention_fa: bad split count %d", n_splits); return AXON_BAD_ARGUMENT; }
+    if (n_splits < 1 || n_splits > FA_MAX_SPLITS || (!decode && n_splits != 1)) { set_error("axon_attention_fa: bad split count %d (1..%d; 1 for prefill tiles)", n_splits, FA_MAX_SPLITS); return AXON_BAD_ARGUMENT; }
     if (n_splits > 1 && scratch == nullptr) { set_error("axon_attention_fa: splits need scratch memory"); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) { set_error("axon_attention_fa: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     FaParams p;

@@ -42,7 +42,7 @@ enum { EPI_STORE_F32 = 0, EPI_STORE_BF16 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 }
 constexpr int SM_ROWS = 16, SM_WARPS = 8, SM_KCHUNK = 64, SM_STAGES = 3;
 
 struct WeightRegs {
-    uint4 lo[2];  // row g:     16 elements k0 + 16t .. + 15
+    uint4 lo[2];  // row g:     elements k0 + 8t .. + 7 and k0 + 32 + 8t .. + 7
     uint4 hi[2];  // row g + 8
 };
 
@@ -56,8 +56,8 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * SM_ROWS;
     const int r_lo = min(row0 + g, N - 1), r_hi = min(row0 + g + 8, N - 1);
-    const __nv_bfloat16* w_lo = w + (long long)r_lo * K + 16 * t;
-    const __nv_bfloat16* w_hi = w + (long long)r_hi * K + 16 * t;
+    const __nv_bfloat16* w_lo = w + (long long)r_lo * K + 8 * t;
+    const __nv_bfloat16* w_hi = w + (long long)r_hi * K + 8 * t;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
     float acc[NT][4];
@@ -67,12 +67,13 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
     auto load_w = [&](WeightRegs& r, int k0) {
-        // k0 + 16t + {0, 8} are the thread's two 8-element pieces; pieces past K read as zero
-        const int ka = k0 + 16 * t;
+        // the thread's two 8-element pieces start at k0 + 8t and k0 + 32 + 8t, so the four
+        // threads of a row read two whole 64-byte runs; pieces past K read as zero
+        const int ka = k0 + 8 * t;
         r.lo[0] = (ka + 8 <= K) ? ldg_stream(w_lo + k0) : zero4;
-        r.lo[1] = (ka + 16 <= K) ? ldg_stream(w_lo + k0 + 8) : zero4;
+        r.lo[1] = (ka + 40 <= K) ? ldg_stream(w_lo + k0 + 32) : zero4;
         r.hi[0] = (ka + 8 <= K) ? ldg_stream(w_hi + k0) : zero4;
-        r.hi[1] = (ka + 16 <= K) ? ldg_stream(w_hi + k0 + 8) : zero4;
+        r.hi[1] = (ka + 40 <= K) ? ldg_stream(w_hi + k0 + 32) : zero4;
     };
 
     const int kstep = SM_WARPS * SM_KCHUNK;
@@ -91,7 +92,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
                 const WeightRegs cur = st[s];
                 if (k_load < K) load_w(st[s], k_load);
                 k_load += kstep;
-                const int ka = kc + 16 * t;
+                const int ka = kc + 8 * t;
                 const uint32_t wl[8] = {cur.lo[0].x, cur.lo[0].y, cur.lo[0].z, cur.lo[0].w,
                                         cur.lo[1].x, cur.lo[1].y, cur.lo[1].z, cur.lo[1].w};
                 const uint32_t wh[8] = {cur.hi[0].x, cur.hi[0].y, cur.hi[0].z, cur.hi[0].w,
@@ -103,7 +104,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
                     if (tok < M) {
                         const __nv_bfloat16* ap = a + (long long)tok * lda + ka;
                         if (ka + 8 <= K) x0 = ldg_cached(ap);
-                        if (ka + 16 <= K) x1 = ldg_cached(ap + 8);
+                        if (ka + 40 <= K) x1 = ldg_cached(ap + 32);
                     }
                     const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll

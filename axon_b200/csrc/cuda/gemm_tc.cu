@@ -236,6 +236,160 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------------------
+// Few activation rows (decode): the operands swap roles.  The weights are the 128-row
+// operand of the MMA and the tokens (padded to NTOK = 16, 32 or 64) its columns, so a
+// CTA streams a 128-row slab of weights through TMA at full width whatever the batch
+// size; the product is bound by reading the weights once from HBM.  To fill the machine
+// when a matrix has few 128-row tiles, K is cut into `splits` slabs, one CTA each: every
+// CTA writes its partial tile to scratch, and the CTA that arrives last at the tile's
+// counter adds the partials in slab order (so the sum does not depend on timing) and
+// applies the epilogue.  In tensor memory a lane is a weight row and a column a token,
+// so for a fixed token the 32 lanes of a warp write 32 consecutive outputs.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int EPI>
+__device__ __forceinline__ void swap_store(float v, int row, int tok, int N, const float* bias, void* out, int ldo) {
+    // v is the product for (weight row, token); all 32 lanes hold consecutive rows
+    if (EPI == TC_SWIGLU) {
+        if (bias && row < N) v += bias[row];
+        const float other = __shfl_xor_sync(0xffffffffu, v, 1);      // row ^ 1: the up value of a gate row
+        if (!(row & 1) && row + 1 < N) {
+            const float r = v / (1.0f + __expf(-v)) * other;
+            ((__nv_bfloat16*)out)[(long long)tok * ldo + (row >> 1)] = __float2bfloat16_rn(r);
+        }
+        return;
+    }
+    if (row >= N) return;
+    if (bias) v += bias[row];
+    const long long o = (long long)tok * ldo + row;
+    if (EPI == TC_STORE_F32) ((float*)out)[o] = v;
+    else if (EPI == TC_STORE_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+    else ((float*)out)[o] += v;
+}
+
+template <int NTOK, int STAGES, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const float* __restrict__ bias, void* __restrict__ out, float* __restrict__ partial,
+                    unsigned int* __restrict__ counters, int M, int N, int K, int ldo, int splits, int per_split) {
+    constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = NTOK * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = NTOK < 32 ? 32 : NTOK;
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ unsigned int arrival;
+    const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(&bars[0]);
+    const uint32_t empty0 = full0 + 8 * STAGES, tmem_full = full0 + 16 * STAGES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / splits, split = blockIdx.x % splits;
+    const int n0 = tile * 128;
+    const int k_total = (K + TC_BK - 1) / TC_BK;
+    const int ks_begin = split * per_split, ks_end = min(k_total, ks_begin + per_split);
+    const int k_stages = ks_end - ks_begin;          // >= 1 by construction of `splits`
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+            for (int i = 0; i < k_stages; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES) mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 0);
+                const uint32_t sw = smem_base + s * STAGE_BYTES, sx = sw + W_BYTES;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(sw, &map_w, (ks_begin + i) * TC_BK, n0, full0 + 8 * s);
+                tma_load_2d(sx, &map_x, (ks_begin + i) * TC_BK, 0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(128, NTOK);
+            for (int i = 0; i < k_stages; ++i) {
+                const int s = i % STAGES;
+                mbar_wait(full0 + 8 * s, (i / STAGES) & 1, 1);
+                tc_fence_after();
+                const uint32_t sw = smem_base + s * STAGE_BYTES, sx = sw + W_BYTES;
+                const uint64_t da = smem_desc(sw), db = smem_desc(sx);
+#pragma unroll
+                for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+                    umma(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i | k) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        mbar_wait(tmem_full, 0, 2);
+        tc_fence_after();
+        const int quarter = warp & 3;
+        const int row = n0 + quarter * 32 + lane;                  // this lane's weight row
+        const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        float acc[NTOK];
+#pragma unroll
+        for (int c = 0; c < NTOK / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + (uint32_t)(c * 16), r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        if (splits == 1) {
+#pragma unroll
+            for (int j = 0; j < NTOK; ++j)
+                if (j < M) swap_store<EPI>(acc[j], row, j, N, bias, out, ldo);
+        } else {
+            // partial[split][token][row of this tile]; then the last CTA of the tile folds
+            float* mine = partial + ((long long)(tile * splits + split) * NTOK) * 128 + quarter * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NTOK; ++j)
+                if (j < M) mine[j * 128] = acc[j];
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps
+            if (threadIdx.x == 64) arrival = atomicAdd(&counters[tile], 1u);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (arrival == (unsigned)(splits - 1)) {
+                __threadfence();
+                const float* all = partial + ((long long)tile * splits * NTOK) * 128 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int j = 0; j < M; ++j) {
+                    float v = 0.f;
+                    for (int s = 0; s < splits; ++s) v += __ldcg(all + ((long long)s * NTOK + j) * 128);
+                    swap_store<EPI>(v, row, j, N, bias, out, ldo);
+                }
+                if (threadIdx.x == 64) counters[tile] = 0u;               // ready for the next launch
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side: tensor maps ---------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -333,6 +487,67 @@ AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void*
     if (!tensor_map(a, M, K, TC_BM, &ma) || !tensor_map(w, N, K, wide ? 256 : 128, &mw)) return AXON_BAD_ARGUMENT;
     if (wide) return launch_tc<256, 4>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
     return launch_tc<128, 6>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
+}
+
+namespace axon {
+template <int NTOK, int STAGES>
+static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
+                       float* partial, unsigned int* counters, int M, int N, int K, int ldo, int tiles, int splits,
+                       int per_split, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (128 * TC_BK * 2 + NTOK * TC_BK * 2) + 1024;
+    const dim3 grid((unsigned)(tiles * splits)), block(192);
+#define AXON_SWAP_LAUNCH(E)                                                                                        \
+    {                                                                                                              \
+        static bool configured = false;                                                                            \
+        if (!configured) {                                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<NTOK, STAGES, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) { set_error("axon_gemm_tc_small: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
+            configured = true;                                                                                     \
+        }                                                                                                          \
+        gemm_tc_swap_kernel<NTOK, STAGES, E><<<grid, block, smem, stream>>>(mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
+    }
+    switch (epi) {
+        case TC_STORE_F32: AXON_SWAP_LAUNCH(TC_STORE_F32) break;
+        case TC_STORE_BF16: AXON_SWAP_LAUNCH(TC_STORE_BF16) break;
+        case TC_RESIDUAL: AXON_SWAP_LAUNCH(TC_RESIDUAL) break;
+        case TC_SWIGLU: AXON_SWAP_LAUNCH(TC_SWIGLU) break;
+        default: set_error("axon_gemm_tc_small: unknown epilogue %d", epi); return AXON_BAD_ARGUMENT;
+    }
+#undef AXON_SWAP_LAUNCH
+    return launch_status("axon_gemm_tc_small");
+}
+}  // namespace axon
+
+// The product for at most 64 activation rows (see gemm_tc_swap_kernel).  `partial` is
+// scratch for split-K partial tiles (`partial_floats` floats; 0 forbids splitting) and
+// `counters` an array of `n_counters` zeroed 32-bit counters that the kernel leaves zeroed.
+// Operands as in axon_gemm_tc.  Calls that share the scratch must not overlap on the GPU.
+AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias, void* out, int epilogue, int M,
+                                int N, int K, int ldo, float* partial, long long partial_floats,
+                                unsigned int* counters, int n_counters, int target_ctas, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return AXON_OK;
+    if (M > 64) { set_error("axon_gemm_tc_small: %d rows; this kernel takes at most 64", M); return AXON_BAD_ARGUMENT; }
+    if (K <= 0 || K % 8) { set_error("axon_gemm_tc_small: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
+    if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc_small: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
+    if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc_small: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
+    const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int tiles = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
+    // as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
+    int splits = 1;
+    if (partial != nullptr && counters != nullptr && tiles <= n_counters && tiles < target_ctas) {
+        splits = (target_ctas + tiles / 2) / tiles;
+        if (splits > k_total / 4) splits = k_total / 4;
+        const long long fit = partial_floats / ((long long)tiles * ntok * 128);
+        if (splits > fit) splits = (int)fit;
+        if (splits < 1) splits = 1;
+    }
+    const int per_split = (k_total + splits - 1) / splits;
+    splits = (k_total + per_split - 1) / per_split;
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, N, K, 128, &mw) || !tensor_map(a, M, K, ntok, &mx)) return AXON_BAD_ARGUMENT;
+    if (ntok == 16) return launch_swap<16, 6>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
+    if (ntok == 32) return launch_swap<32, 5>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
+    return launch_swap<64, 4>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
 }
 
 // 0 when no kernel of this file ever gave up on a wait; else 1 + the role (0 producer,

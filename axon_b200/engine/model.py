@@ -22,6 +22,8 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
         spec.validate()
         self.spec, self.rt = spec, rt
+        #: whether every part only queues kernels (then steps may be captured into CUDA graphs)
+        self.graph_safe = True
         uses: Dict[str, int] = {}
         for category, ps in _walk(spec):
             for name in ps.weights.values():
@@ -29,6 +31,7 @@ class DecoderModel:
 
         def build(category: str, ps: PartSpec) -> Part:
             cls = part_class(category, ps.kind)
+            self.graph_safe = self.graph_safe and bool(cls.graph_safe)
             nested = getattr(cls, "nested", {})
             tensors = {}
             for local in cls.tensors(ps):
@@ -57,7 +60,8 @@ class DecoderModel:
         e = self.spec.schedule[entry]
         return entry if e.cache_of is None else e.cache_of
 
-    def forward(self, ctx: StepContext, cache: Any, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
+    def forward(self, ctx: StepContext, cache: Any, want_rows: Optional[torch.Tensor], n_want: int,
+                logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the step's tokens through every schedule entry; the float32 logits of
         the wanted rows ``[n_want, vocab]`` (None when nothing is wanted)."""
         rt, n = self.rt, ctx.n_tokens
@@ -70,7 +74,10 @@ class DecoderModel:
         # the head runs on the wanted rows only (src/lm.rs:114-126)
         h = rt.buffer("head_in", (n_want, self.spec.hidden_size))
         self.final_norm.forward(x, h, rows=want_rows)
-        logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        if logits_out is not None:
+            logits = logits_out[:n_want]
+        else:
+            logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         self.head.forward(h, logits)
         return logits
 

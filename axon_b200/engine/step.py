@@ -22,6 +22,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import PagedCache
+from ..kernels import lib
 from ..parts.base import Runtime, StepContext
 from .model import DecoderModel
 
@@ -51,7 +52,15 @@ class Engine:
         self._staging: List[torch.Tensor] = []
         self._events: List[Optional[torch.cuda.Event]] = []
         self._turn = 0
-        #: kernels launched and steps run, for reports
+        #: decode-only steps replay captured CUDA graphs (one per batch size, number of wanted
+        #: rows and attention split count), as the reference captures its decode step
+        #: (src/cuda/qwen2.rs:2978-3011; per step shape: src/cuda/qwen2/slots.rs:722-785)
+        self.cuda_graphs = bool(model.graph_safe)
+        self.graph_max_batch = 256
+        self.graph_cache_size = 64
+        self._graphs = {}
+        self._graph_generation = self.rt.generation
+        #: steps run, for reports
         self.steps = 0
 
     # -- requests ---------------------------------------------------------
@@ -117,12 +126,13 @@ class Engine:
 
         s = len(entries)
         n_want = sum(len(e.want) for e in entries)
-        total = 3 * n + 4 * s + n_want
+        decode_only = n == s                      # one token per entry
+        total = 3 * n + 4 * s + n_want + (2 * s if decode_only else 0)
         stage = self._stage(total)
         buf = stage.numpy()
         tokens, positions, slots = buf[0:n], buf[n:2 * n], buf[2 * n:3 * n]
         seg = buf[3 * n:3 * n + 4 * s].reshape(4, s)
-        want = buf[3 * n + 4 * s: total]
+        want = buf[3 * n + 4 * s: 3 * n + 4 * s + n_want]
         at = w_at = 0
         seg_slot, seg_q_start, seg_q_len, seg_kv_len = [], [], [], []
         for i, (e, start) in enumerate(zip(entries, starts)):
@@ -136,21 +146,74 @@ class Engine:
                 want[w_at] = at + int(w)
                 w_at += 1
             at += k
-        dev = self.rt.buffer("step_meta", (total,), torch.int32)
+        if decode_only:
+            # one work item per entry for the attention kernels: (segment, first token 0)
+            items = buf[total - 2 * s: total].reshape(s, 2)
+            items[:, 0] = np.arange(s, dtype=np.int32)
+            items[:, 1] = 0
+
+        # A decode-only step of a shape seen before replays a captured CUDA graph: every
+        # kernel argument that depends on the host is in the key, everything else
+        # (tokens, positions, slots, lengths, block tables) is read from device memory.
+        graph_key = None
+        if self.cuda_graphs and decode_only and n <= self.graph_max_batch:
+            graph_key = (n, n_want, min(32, -(-max(seg_kv_len) // 64)))
+        meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{graph_key[0]}_{graph_key[1]}"
+        dev = self.rt.buffer(meta_name, (total,), torch.int32)
         dev.copy_(stage[:total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._events[self._cur] = ev
         cache.sync_tables()
 
-        ctx = StepContext(
-            rt=self.rt, n_tokens=n, tokens=dev[0:n], positions=dev[n:2 * n], token_slot=dev[2 * n:3 * n],
-            seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len,
-            segments=dev[3 * n:3 * n + 4 * s].view(4, s),
-            host_positions=positions.tolist())
-        want_rows = dev[3 * n + 4 * s: total] if n_want else None
-        logits = self.model.forward(ctx, cache, want_rows, n_want)
+        def context() -> StepContext:
+            return StepContext(
+                rt=self.rt, n_tokens=n, tokens=dev[0:n], positions=dev[n:2 * n], token_slot=dev[2 * n:3 * n],
+                seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len,
+                segments=dev[3 * n:3 * n + 4 * s].view(4, s),
+                unit_items=dev[total - 2 * s: total] if decode_only else None,
+                host_positions=positions.tolist())
+        want_rows = dev[3 * n + 4 * s: 3 * n + 4 * s + n_want] if n_want else None
+
+        if graph_key is None:
+            logits = self.model.forward(context(), cache, want_rows, n_want)
+        else:
+            logits = self._graph_step(graph_key, context, want_rows, n_want)
         for e, start in zip(entries, starts):
             cache.commit(e.slot, start + len(e.tokens))
         self.steps += 1
         return logits
+
+    def _graph_step(self, key, context, want_rows, n_want) -> Optional[torch.Tensor]:
+        """Run a decode-only step through its CUDA graph, capturing it the first time.
+        The logits live in a buffer of the graph: they are valid until the next step."""
+        if self._graph_generation != self.rt.generation:
+            self._graphs.clear()              # a scratch buffer moved: captured addresses are stale
+            self._graph_generation = self.rt.generation
+        out = self.rt.buffer(f"graph_logits_{n_want}", (max(n_want, 1), self.model.spec.vocab_size), torch.float32)
+        entry = self._graphs.get(key)
+        if entry is not None:
+            graph, launches = entry
+            graph.replay()
+            lib.add_launches(launches)
+            return out[:n_want] if n_want else None
+        # first time: run it plainly (this also sizes every scratch buffer), then record it
+        self.model.forward(context(), self.cache, want_rows, n_want, logits_out=out)
+        if self._graph_generation == self.rt.generation:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                before = lib.launch_count()
+                with torch.cuda.graph(graph):
+                    self.model.forward(context(), self.cache, want_rows, n_want, logits_out=out)
+                launches = lib.launch_count() - before
+                lib.add_launches(-launches)       # recorded, not run
+                if self._graph_generation == self.rt.generation:
+                    if len(self._graphs) >= self.graph_cache_size:
+                        self._graphs.pop(next(iter(self._graphs)))
+                    self._graphs[key] = (graph, launches)
+            except RuntimeError:
+                # capture failed (for instance a part that allocates): steps of this shape stay eager
+                self.cuda_graphs = False
+        else:
+            self._graph_generation = self.rt.generation
+        return out[:n_want] if n_want else None

@@ -18,11 +18,42 @@ EPI_STORE_F32, EPI_STORE_BF16, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SMALL_M = 64
 
 #: switches for tests that compare a tuned kernel with the plain one
-ENABLED = {"gemm_small_m": True, "gemm_tc": True, "attention_prefill": True, "attention_decode": True}
+ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attention_prefill": True,
+           "attention_decode": True}
 
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+_SPLIT_SCRATCH = {}
+
+
+def _split_scratch(device: torch.device):
+    """Scratch of the split-K products of one device: partial tiles (about two CTAs per SM
+    times 64 tokens times 128 rows) and zeroed tile counters that the kernel leaves zeroed."""
+    got = _SPLIT_SCRATCH.get(device)
+    if got is None:
+        got = (torch.empty(2 * 2 * SM_COUNT * 64 * 128, dtype=torch.float32, device=device),
+               torch.zeros(1024, dtype=torch.int32, device=device))
+        _SPLIT_SCRATCH[device] = got
+    return got
+
+
+def _gemm_small(a, w, bias, out, epi, M, N, K) -> bool:
+    """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one."""
+    if ENABLED["gemm_tc_small"]:
+        partial, counters = _split_scratch(a.device)
+        check(lib.cuda().axon_gemm_tc_small(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
+                                            out.data_ptr(), epi, M, N, K, out.stride(0), partial.data_ptr(),
+                                            partial.numel(), counters.data_ptr(), counters.numel(), 2 * SM_COUNT,
+                                            _stream()))
+        return True
+    if ENABLED["gemm_small_m"]:
+        check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
+                                           out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
+        return True
+    return False
 
 
 def _bf16_operands(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -46,9 +77,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         epi = EPI_STORE_BF16
     else:
         return False
-    if M <= SMALL_M and ENABLED["gemm_small_m"]:
-        check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
-                                           out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
+    if M <= SMALL_M and _gemm_small(a, w, bias, out, epi, M, N, K):
         return True
     if ENABLED["gemm_tc"]:
         check(lib.cuda().axon_gemm_tc(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
@@ -67,9 +96,7 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
         return False
     M, K = h.shape
     N = w_gate_up.shape[0]
-    if M <= SMALL_M and ENABLED["gemm_small_m"]:
-        check(lib.cuda().axon_gemm_small_m(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,
-                                           M, N, K, K, act.stride(0), _stream()))
+    if M <= SMALL_M and _gemm_small(h, w_gate_up, None, act, EPI_SWIGLU, M, N, K):
         return True
     if ENABLED["gemm_tc"]:
         check(lib.cuda().axon_gemm_tc(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,
@@ -79,6 +106,7 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
 
 
 FA_HEAD_DIMS = (16, 32, 64, 128)
+FA_MAX_SPLITS = 32
 SM_COUNT = 148
 
 
@@ -91,6 +119,14 @@ def _attention_items(ctx, group: int):
     if got is not None:
         return got
     tpt_dec, tpt_pre = (16 // group if group <= 16 else 0), 64 // group
+    if ctx.unit_items is not None:
+        # single tokens only: the step brought its work list (segment, 0) along
+        n = len(ctx.seg_q_len)
+        got = {"dec": ctx.unit_items if tpt_dec else None, "n_dec": n if tpt_dec else 0, "dec_kv": ctx.max_kv_len,
+               "pre": None if tpt_dec else ctx.unit_items, "n_pre": 0 if tpt_dec else n,
+               "tpt_dec": tpt_dec, "tpt_pre": tpt_pre}
+        ctx.scratch[key] = got
+        return got
     dec, pre = [], []
     dec_kv = 0
     for s, (n, kv_len) in enumerate(zip(ctx.seg_q_len, ctx.seg_kv_len)):
@@ -124,10 +160,13 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     n_seg = len(ctx.seg_slot)
     if it["n_dec"]:
         tiles = -(-it["dec_kv"] // 64)
-        splits = max(1, min(tiles, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads))))
+        splits = max(1, min(tiles, FA_MAX_SPLITS, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads))))
         scratch = None
         if splits > 1:
-            scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * splits * 16 * (kv.head_dim + 2),),
+            # sized for the most splits this batch can get, so that the buffer never moves
+            # while the contexts grow (captured graphs hold its address)
+            most = min(FA_MAX_SPLITS, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads)))
+            scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * most * 16 * (kv.head_dim + 2),),
                                     torch.float32)
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
                                    it["dec"].data_ptr(), it["n_dec"], kv._ref, heads, float(scale), int(kv.window),

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "axon_gemm_small_m": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_tc": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_tc_status": [],
+    "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P],
 }
@@ -134,6 +135,13 @@ def launch_count() -> int:
     """How many kernel launchers of the library have been called so far (each launches
     its kernels on the current stream; benches report the difference over a region)."""
     return _launches
+
+
+def add_launches(n: int) -> None:
+    """Count launches that did not go through a launcher call: a replayed CUDA graph
+    launches every kernel that was captured into it."""
+    global _launches
+    _launches += n
 
 
 def check(status: int) -> None:

@@ -46,6 +46,9 @@ class Runtime:
         #: the true 32-bit path: plain FFMA kernels everywhere
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
+        #: raised whenever an existing scratch buffer is replaced by a larger one: addresses
+        #: handed out before are stale from then on (captured CUDA graphs must be dropped)
+        self.generation = 0
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         dtype = dtype or self.dtype
@@ -54,6 +57,8 @@ class Runtime:
             n *= s
         buf = self._buffers.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if buf is not None:
+                self.generation += 1
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
         return buf[:n].view(shape)
@@ -84,6 +89,9 @@ class StepContext:
     seg_kv_len: List[int]
     #: device copy of the four lists above as int32 ``[4, segments]`` (slot, q_start, q_len, kv_len)
     segments: Optional[torch.Tensor] = None
+    #: for steps of single tokens: device int32 ``[segments, 2]`` rows ``(segment, 0)``, the
+    #: attention kernels' work list (so that such a step needs no further host-to-device copy)
+    unit_items: Optional[torch.Tensor] = None
     #: host copies for parts that run on the host side of a step (toy parts, tests)
     host_positions: Optional[List[int]] = None
     scratch: Dict[Any, Any] = field(default_factory=dict)
@@ -100,6 +108,11 @@ class StepContext:
 class Part:
     category: ClassVar[str] = ""
     kind: ClassVar[str] = ""
+    #: True when ``forward`` only queues kernels on the current stream with arguments that
+    #: do not depend on values read back from the device: no synchronisation, no host-side
+    #: branching on device data, no allocation.  Steps of a model whose parts are all safe
+    #: may be captured into CUDA graphs.
+    graph_safe: ClassVar[bool] = False
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:

@@ -28,6 +28,7 @@ class RMSNorm(Part):
     """
 
     category, kind = "norm", "rmsnorm"
+    graph_safe = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -56,6 +57,7 @@ class RotaryEncoding(Part):
     """
 
     category, kind = "position", "rope"
+    graph_safe = True
 
     def __init__(self, spec, tensors, rt, build):
         super().__init__(spec, tensors, rt, build)
@@ -103,6 +105,7 @@ class Attention(Mixer):
     """
 
     category, kind = "mixer", "attention"
+    graph_safe = True
     nested = {"position": "position"}
 
     @classmethod
@@ -167,6 +170,7 @@ class SwiGLU(FeedForward):
     """
 
     category, kind = "ffn", "swiglu"
+    graph_safe = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -192,6 +196,7 @@ class PreNormBlock(Part):
     (src/model.rs:2955-3060)."""
 
     category, kind = "block", "prenorm"
+    graph_safe = True
     nested = {"norm_mixer": "norm", "mixer": "mixer", "norm_ffn": "norm", "ffn": "ffn"}
 
     def __init__(self, spec, tensors, rt, build):
@@ -215,6 +220,7 @@ class Embedding(Part):
     (src/model.rs:2657-2675).  params: ``vocab_size``, ``hidden_size``; tensors: ``table``."""
 
     category, kind = "embedding", "embedding"
+    graph_safe = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -235,6 +241,7 @@ class LinearHead(Part):
     params: ``vocab_size``, ``hidden_size``; tensors: ``weight``."""
 
     category, kind = "head", "linear_head"
+    graph_safe = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:

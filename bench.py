@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_7B["num_hidden_layers"],
                     help="run fewer layers than the 28 of the configuration (both numbers go into `config`)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points")
+    ap.add_argument("--skip-prefill", action="store_true", help="leave out the prefill measurement (for profiles)")
+    ap.add_argument("--prefill-only", action="store_true", help="run the prefill measurement alone (for profiles)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -202,6 +204,28 @@ def main() -> int:
                 "launches": launches, "bytes": weight_bytes + b * ctx_mid * kv_bytes_per_pos,
                 "clocks": sampler.summary() if sampler else None}
 
+    def time_prefill(T, repeats=3):
+        """One request, T tokens in one step; the best of the repeats after the first."""
+        ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+        pms = []
+        for it in range(repeats):
+            with net.new_cache() as c:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                engine.step([StepEntry(c.slot, ptoks, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                pms.append(e0.elapsed_time(e1))
+            engine.cache.flush()
+        pm = min(pms[1:]) if len(pms) > 1 else pms[0]
+        flops = 2 * L * layer_params * T + 2 * V * D + L * 2 * 2 * H * hd * T * (T + 1) / 2
+        return {"value": round(T / (pm / 1e3), 1), "tokens": T, "ms": round(pm, 3),
+                "frac": round(flops / (pm / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+
+    if args.prefill_only:
+        print(json.dumps({"prefill": time_prefill(args.prefill_tokens, max(2, args.steps))}))
+        return 0
     main_r = time_decode(args.batch, args.steps, args.warmup, with_clocks=True)
     points = {}
     if not args.skip_points:
@@ -209,25 +233,7 @@ def main() -> int:
             r = time_decode(b, max(8, args.steps // 4), 3)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
-
-    # prefill: one request, --prefill-tokens tokens in one step
-    T = args.prefill_tokens
-    ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
-    pms = []
-    for it in range(3):
-        with net.new_cache() as c:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            e0.record()
-            engine.step([StepEntry(c.slot, ptoks, [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            pms.append(e0.elapsed_time(e1))
-        engine.cache.flush()
-    pm = min(pms[1:]) if len(pms) > 1 else pms[0]
-    prefill_flops = 2 * L * layer_params * T + 2 * V * D + L * 2 * 2 * H * hd * T * (T + 1) / 2
-    prefill = {"value": round(T / (pm / 1e3), 1), "tokens": T, "ms": round(pm, 3),
-               "frac": round(prefill_flops / (pm / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+    prefill = None if args.skip_prefill else time_prefill(args.prefill_tokens)
 
     step_s = main_r["ms_per_step"] / 1e3
     achieved = main_r["bytes"] / step_s / 1e9

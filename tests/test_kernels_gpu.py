@@ -315,9 +315,20 @@ def test_residual_add_and_convert(ops, dtype):
 # ---------------------------------------------------------------------------
 # the tuned bfloat16 kernels, each against float64
 
+@pytest.fixture(params=["tcgen05_swapped", "mma_sync"])
+def small_m_kernel(request):
+    """Both kernels for at most 64 rows, one at a time."""
+    from axon_b200.kernels import fast
+    old = fast.ENABLED["gemm_tc_small"]
+    fast.ENABLED["gemm_tc_small"] = request.param == "tcgen05_swapped"
+    yield request.param
+    fast.ENABLED["gemm_tc_small"] = old
+
+
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 23, 32, 33, 64])
-@pytest.mark.parametrize("N,K", [(16, 64), (2, 8), (33, 24), (1000, 160), (344, 344), (130, 1096), (4608, 3584)])
-def test_gemm_small_m(ops, M, N, K):
+@pytest.mark.parametrize("N,K", [(16, 64), (2, 8), (33, 24), (1000, 160), (344, 344), (130, 1096), (4608, 3584),
+                                 (3584, 18944)])
+def test_gemm_small_m(ops, small_m_kernel, M, N, K):
     from axon_b200.kernels import fast
     a = rand(M, K, dtype=torch.bfloat16, seed=70)
     w = rand(N, K, dtype=torch.bfloat16, seed=71, std=0.1)
@@ -340,6 +351,7 @@ def test_gemm_small_m(ops, M, N, K):
         assert fast.gemm_swiglu(a, w, act)
         g, u = want[:, 0::2], want[:, 1::2]
         close(act, g / (1 + torch.exp(-g)) * u, OUT_TOL[torch.bfloat16], "SwiGLU epilogue")
+    assert fast.gemm_tc_status() == 0, "a wait inside a tensor-core kernel gave up"
 
 
 def test_gemm_small_m_refusals(ops):
