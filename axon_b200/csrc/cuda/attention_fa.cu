@@ -97,6 +97,8 @@ attention_fa_kernel(const FaParams p) {
     constexpr int NT_S = DECODE ? 2 : 8;      // 8-key score tiles per warp
     constexpr int NT_O = HD / 8;              // 8-dim output tiles
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();          // queries and this step's keys come from the kernels before
     const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t q_sm = smem;
     const uint32_t k_sm = q_sm + BM * HD * 2;
@@ -301,6 +303,8 @@ attention_fa_kernel(const FaParams p) {
 // Fold the splits of each (item, kv head, row) in ascending order and normalise.
 template <int HD>
 __global__ void attention_combine_kernel(const FaParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int item = blockIdx.x, kvh = blockIdx.y;
     const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
     const int q_start = p.segments[p.n_segments + seg], q_len = p.segments[2 * p.n_segments + seg];
@@ -349,11 +353,11 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
         configured = true;
     }
     dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);
-    attention_fa_kernel<HD, DECODE><<<grid, FA_THREADS, smem, stream>>>(p);
+    launch_pdl(attention_fa_kernel<HD, DECODE>, grid, dim3(FA_THREADS), smem, stream, p);
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
     if (DECODE && p.n_splits > 1) {
-        attention_combine_kernel<HD><<<dim3(n_items, kv_heads), 128, 0, stream>>>(p);
+        launch_pdl(attention_combine_kernel<HD>, dim3(n_items, kv_heads), dim3(128), 0, stream, p);
         st = launch_status("axon_attention_fa combine");
     }
     return st;

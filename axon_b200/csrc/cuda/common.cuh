@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 #define AXON_API extern "C" __attribute__((visibility("default")))
 
 // Status codes returned by every launcher.

@@ -52,6 +52,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
                     const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int lda,
                     int ldo) {
     __shared__ float red[SM_WARPS][SM_ROWS][NT * 8 + 1];
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * SM_ROWS;
@@ -84,6 +85,8 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
         if (k_load < K) load_w(st[s], k_load);
         k_load += kstep;
     }
+    // the weights above do not depend on the kernel before this one; the activations do
+    pdl_wait();
     for (int k0 = warp * SM_KCHUNK; k0 < K; k0 += SM_STAGES * kstep) {
 #pragma unroll
         for (int s = 0; s < SM_STAGES; ++s) {
@@ -164,10 +167,10 @@ static int launch_small_m(int epi, const void* a, const void* w, const float* bi
     const __nv_bfloat16* ap = (const __nv_bfloat16*)a;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
     switch (epi) {
-        case EPI_STORE_F32: gemm_small_m_kernel<NT, EPI_STORE_F32><<<grid, block, 0, stream>>>(ap, wp, bias, out, M, N, K, lda, ldo); break;
-        case EPI_STORE_BF16: gemm_small_m_kernel<NT, EPI_STORE_BF16><<<grid, block, 0, stream>>>(ap, wp, bias, out, M, N, K, lda, ldo); break;
-        case EPI_RESIDUAL: gemm_small_m_kernel<NT, EPI_RESIDUAL><<<grid, block, 0, stream>>>(ap, wp, bias, out, M, N, K, lda, ldo); break;
-        case EPI_SWIGLU: gemm_small_m_kernel<NT, EPI_SWIGLU><<<grid, block, 0, stream>>>(ap, wp, bias, out, M, N, K, lda, ldo); break;
+        case EPI_STORE_F32: launch_pdl(gemm_small_m_kernel<NT, EPI_STORE_F32>, grid, block, 0, stream, ap, wp, bias, out, M, N, K, lda, ldo); break;
+        case EPI_STORE_BF16: launch_pdl(gemm_small_m_kernel<NT, EPI_STORE_BF16>, grid, block, 0, stream, ap, wp, bias, out, M, N, K, lda, ldo); break;
+        case EPI_RESIDUAL: launch_pdl(gemm_small_m_kernel<NT, EPI_RESIDUAL>, grid, block, 0, stream, ap, wp, bias, out, M, N, K, lda, ldo); break;
+        case EPI_SWIGLU: launch_pdl(gemm_small_m_kernel<NT, EPI_SWIGLU>, grid, block, 0, stream, ap, wp, bias, out, M, N, K, lda, ldo); break;
         default: set_error("axon_gemm_small_m: unknown epilogue %d", epi); return AXON_BAD_ARGUMENT;
     }
     return launch_status("axon_gemm_small_m");

@@ -296,6 +296,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int k_total = (K + TC_BK - 1) / TC_BK;
     const int ks_begin = split * per_split, ks_end = min(k_total, ks_begin + per_split);
     const int k_stages = ks_end - ks_begin;          // >= 1 by construction of `splits`
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -316,9 +317,19 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-            for (int i = 0; i < k_stages; ++i) {
+            // the weights do not depend on the kernel before this one: start streaming them
+            // into every stage, and wait for that kernel only before the activations
+            const int ahead = k_stages < STAGES ? k_stages : STAGES;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(smem_base + i * STAGE_BYTES, &map_w, (ks_begin + i) * TC_BK, n0, full0 + 8 * i);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(smem_base + i * STAGE_BYTES + W_BYTES, &map_x, (ks_begin + i) * TC_BK, 0, full0 + 8 * i);
+            for (int i = ahead; i < k_stages; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES) mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 0);
+                mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 0);
                 const uint32_t sw = smem_base + s * STAGE_BYTES, sx = sw + W_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(sw, &map_w, (ks_begin + i) * TC_BK, n0, full0 + 8 * s);
@@ -342,6 +353,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             umma_commit(tmem_full);
         }
     } else {
+        pdl_wait();                                                // before anything is written
         mbar_wait(tmem_full, 0, 2);
         tc_fence_after();
         const int quarter = warp & 3;
@@ -504,7 +516,7 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
             if (e != cudaSuccess) { set_error("axon_gemm_tc_small: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
             configured = true;                                                                                     \
         }                                                                                                          \
-        gemm_tc_swap_kernel<NTOK, STAGES, E><<<grid, block, smem, stream>>>(mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
+        launch_pdl(gemm_tc_swap_kernel<NTOK, STAGES, E>, grid, block, smem, stream, mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_SWAP_LAUNCH(TC_STORE_F32) break;

@@ -26,6 +26,8 @@ void set_error(const char* fmt, ...) {
 template <typename T>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ x, int dim, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const long long row = tokens[t];
     for (int d = threadIdx.x; d < dim; d += blockDim.x)
@@ -40,6 +42,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int32_t* __restrict__ rows, TO* __restrict__ out, int dim,
                                float eps, int unit_offset) {
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const long long r_in = rows ? rows[blockIdx.x] : blockIdx.x;
     const float* xr = x + r_in * dim;
     float ss = 0.f;
@@ -136,6 +140,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ act
 __global__ void rope_table_kernel(const int32_t* __restrict__ positions,
                                   const double* __restrict__ inv_freq, float2* __restrict__ table,
                                   int n, int half, float magnitude) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n * half) return;
     const int t = i / half, f = i % half;
@@ -156,6 +162,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
                                      const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
                                      T* __restrict__ pool, PagedKv kv, int heads, int rot, int adjacent,
                                      int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int hd = kv.head_dim, half = hd / 2, rhalf = rot / 2;
     const int q_dim = heads * hd, kv_dim = kv.kv_heads * hd;
@@ -321,9 +329,9 @@ AXON_API int axon_embed(const int32_t* tokens, const void* table, int table_dtyp
     if (n <= 0) return AXON_OK;
     const int threads = dim >= 1024 ? 256 : 128;
     if (table_dtype == AXON_F32)
-        embed_kernel<float><<<n, threads, 0, stream>>>(tokens, (const float*)table, x, dim, scale);
+        launch_pdl(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, tokens, (const float*)table, x, dim, scale);
     else if (table_dtype == AXON_BF16)
-        embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, dim, scale);
+        launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, x, dim, scale);
     else { set_error("axon_embed: unknown table dtype %d", table_dtype); return AXON_BAD_ARGUMENT; }
     return launch_status("axon_embed");
 }
@@ -335,9 +343,9 @@ AXON_API int axon_rmsnorm(const float* x, const float* gain, const int32_t* rows
     int threads = 128;
     while (threads < 1024 && threads * 4 < dim) threads *= 2;
     if (out_dtype == AXON_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, gain, rows, (float*)out, dim, eps, unit_offset);
+        launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (float*)out, dim, eps, unit_offset);
     else if (out_dtype == AXON_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, dim, eps, unit_offset);
+        launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (__nv_bfloat16*)out, dim, eps, unit_offset);
     else { set_error("axon_rmsnorm: unknown output dtype %d", out_dtype); return AXON_BAD_ARGUMENT; }
     return launch_status("axon_rmsnorm");
 }
@@ -383,7 +391,7 @@ AXON_API int axon_rope_table(const int32_t* positions, const double* inv_freq, f
                              int half, float magnitude, cudaStream_t stream) {
     if (n <= 0 || half <= 0) return AXON_OK;
     const int total = n * half;
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)table, n, half, magnitude);
+    launch_pdl(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)table, n, half, magnitude);
     return launch_status("axon_rope_table");
 }
 
@@ -398,9 +406,9 @@ AXON_API int axon_rope_kv_write(const float* qkv, const float* table, const int3
     dim3 grid(n, (items + 255) / 256 > 8 ? 8 : (items + 255) / 256);
     PagedKv kv = to_paged(layout);
     if (dtype == AXON_F32)
-        rope_kv_write_kernel<float><<<grid, 256, 0, stream>>>(qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv);
+        launch_pdl(rope_kv_write_kernel<float>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv);
     else if (dtype == AXON_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(qkv, (const float2*)table, positions, token_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, kv, heads, rot, adjacent, write_kv);
+        launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, kv, heads, rot, adjacent, write_kv);
     else { set_error("axon_rope_kv_write: unknown dtype %d", dtype); return AXON_BAD_ARGUMENT; }
     return launch_status("axon_rope_kv_write");
 }

@@ -44,6 +44,8 @@ __device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v
 __global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ best, int vocab,
                               long long row_stride) {
     __shared__ unsigned long long sm[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (long long)blockIdx.x * row_stride;
     unsigned long long k = 0;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -229,7 +231,7 @@ AXON_API int axon_argmax(const float* logits, int32_t* best, int rows, int vocab
                          cudaStream_t stream) {
     if (rows <= 0) return AXON_OK;
     if (vocab <= 0) { set_error("axon_argmax: empty rows"); return AXON_BAD_ARGUMENT; }
-    argmax_kernel<<<rows, 1024, 0, stream>>>(logits, best, vocab, row_stride);
+    launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, best, vocab, row_stride);
     return launch_status("axon_argmax");
 }
 
