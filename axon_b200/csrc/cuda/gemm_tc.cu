@@ -171,13 +171,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (m >= M || nc >= N) continue;
             if (EPI == TC_SWIGLU) {
                 __nv_bfloat16* dst = (__nv_bfloat16*)out + (long long)m * ldo + (nc >> 1);
+                float res[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    if (nc + 2 * i + 1 < N) {
-                        float gv = __uint_as_float(r[2 * i]), uv = __uint_as_float(r[2 * i + 1]);
-                        if (bias) { gv += bias[nc + 2 * i]; uv += bias[nc + 2 * i + 1]; }
-                        dst[i] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                    float gv = __uint_as_float(r[2 * i]), uv = __uint_as_float(r[2 * i + 1]);
+                    if (bias && nc + 2 * i + 1 < N) { gv += bias[nc + 2 * i]; uv += bias[nc + 2 * i + 1]; }
+                    res[i] = gv / (1.0f + __expf(-gv)) * uv;
+                }
+                if (nc + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(res[2 * i], res[2 * i + 1]);
+                        pk[i] = *reinterpret_cast<uint32_t*>(&v);
                     }
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (nc + 2 * i + 1 < N) dst[i] = __float2bfloat16_rn(res[i]);
                 }
             } else if (EPI == TC_STORE_BF16) {
                 __nv_bfloat16* dst = (__nv_bfloat16*)out + (long long)m * ldo + nc;
@@ -204,15 +217,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 float* dst = (float*)out + (long long)m * ldo + nc;
                 const bool full = (nc + 32 <= N) && ((((uintptr_t)dst) & 15) == 0);
                 if (full) {
+                    // what the residual epilogue adds to is loaded before any store of the chunk,
+                    // so that the eight loads are in flight together
+                    float4 o[8];
+                    if (EPI == TC_RESIDUAL) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = *reinterpret_cast<const float4*>(dst + 4 * i);
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                                __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
                         if (bias) { v.x += bias[nc + 4 * i]; v.y += bias[nc + 4 * i + 1]; v.z += bias[nc + 4 * i + 2]; v.w += bias[nc + 4 * i + 3]; }
-                        if (EPI == TC_RESIDUAL) {
-                            const float4 o = *reinterpret_cast<const float4*>(dst + 4 * i);
-                            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                        }
+                        if (EPI == TC_RESIDUAL) { v.x += o[i].x; v.y += o[i].y; v.z += o[i].z; v.w += o[i].w; }
                         *reinterpret_cast<float4*>(dst + 4 * i) = v;
                     }
                 } else {
@@ -255,8 +272,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// What the residual epilogue adds to: loaded ahead of the stores, many at a time, because
+// a load behind a store to the same array cannot be moved up by the compiler and a chain
+// of dependent global loads is what small kernels spend their time on.
 template <int EPI>
-__device__ __forceinline__ void swap_store(float v, int row, int tok, int N, const float* bias, void* out, int ldo) {
+__device__ __forceinline__ float swap_old(int row, int tok, int N, const void* out, int ldo) {
+    if (EPI != TC_RESIDUAL || row >= N) return 0.f;
+    return ((const float*)out)[(long long)tok * ldo + row];
+}
+
+template <int EPI>
+__device__ __forceinline__ void swap_store(float v, float old, int row, int tok, int N, const float* bias, void* out,
+                                           int ldo) {
     // v is the product for (weight row, token); all 32 lanes hold consecutive rows
     if (EPI == TC_SWIGLU) {
         if (bias && row < N) v += bias[row];
@@ -272,16 +299,19 @@ __device__ __forceinline__ void swap_store(float v, int row, int tok, int N, con
     const long long o = (long long)tok * ldo + row;
     if (EPI == TC_STORE_F32) ((float*)out)[o] = v;
     else if (EPI == TC_STORE_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
-    else ((float*)out)[o] += v;
+    else ((float*)out)[o] = old + v;
 }
 
-template <int NTOK, int STAGES, int EPI>
+// R: 128-row sub-tiles per CTA (1 or 2).  Two halve the number of CTAs of a matrix with
+// many rows, so that one CTA per SM covers it and the next kernel's CTAs fit beside it
+// to preload their weights; splitting K is for R == 1 only.
+template <int NTOK, int STAGES, int EPI, int R>
 __global__ void __launch_bounds__(192)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const float* __restrict__ bias, void* __restrict__ out, float* __restrict__ partial,
                     unsigned int* __restrict__ counters, int M, int N, int K, int ldo, int splits, int per_split) {
-    constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = NTOK * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
-    constexpr uint32_t TMEM_COLS = NTOK < 32 ? 32 : NTOK;
+    constexpr uint32_t W_BYTES = R * 128 * TC_BK * 2, X_BYTES = NTOK * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = R * NTOK < 32 ? 32 : R * NTOK;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
@@ -292,7 +322,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / splits, split = blockIdx.x % splits;
-    const int n0 = tile * 128;
+    const int n0 = tile * 128 * R;
     const int k_total = (K + TC_BK - 1) / TC_BK;
     const int ks_begin = split * per_split, ks_end = min(k_total, ks_begin + per_split);
     const int k_stages = ks_end - ks_begin;          // >= 1 by construction of `splits`
@@ -347,7 +377,10 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const uint64_t da = smem_desc(sw), db = smem_desc(sx);
 #pragma unroll
                 for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
-                    umma(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i | k) ? 1u : 0u);
+#pragma unroll
+                    for (int r = 0; r < R; ++r)   // sub-tile r: 128 rows further (16 KiB), NTOK columns further
+                        umma(tmem_acc + (uint32_t)(r * NTOK), da + (uint64_t)(r * 1024 + 2 * k), db + (uint64_t)(2 * k),
+                             idesc, (i | k) ? 1u : 0u);
                 umma_commit(empty0 + 8 * s);
             }
             umma_commit(tmem_full);
@@ -357,8 +390,27 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_wait(tmem_full, 0, 2);
         tc_fence_after();
         const int quarter = warp & 3;
-        const int row = n0 + quarter * 32 + lane;                  // this lane's weight row
         const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        if (R > 1) {
+            // whole-K sub-tiles, one after the other
+#pragma unroll 1
+            for (int r = 0; r < R; ++r) {
+                const int row_r = n0 + r * 128 + quarter * 32 + lane;
+#pragma unroll
+                for (int c = 0; c < NTOK / 16; ++c) {
+                    uint32_t v[16];
+                    float old[16];
+                    tmem_ld16(lane_addr + (uint32_t)(r * NTOK + c * 16), v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) old[i] = (c * 16 + i < M) ? swap_old<EPI>(row_r, c * 16 + i, N, out, ldo) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (c * 16 + i < M) swap_store<EPI>(__uint_as_float(v[i]), old[i], row_r, c * 16 + i, N, bias, out, ldo);
+                }
+            }
+            tc_fence_before();
+        } else {
+        const int row = n0 + quarter * 32 + lane;                  // this lane's weight row
         float acc[NTOK];
 #pragma unroll
         for (int c = 0; c < NTOK / 16; ++c) {
@@ -369,9 +421,12 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         tc_fence_before();
         if (splits == 1) {
+            float old[NTOK];
+#pragma unroll
+            for (int j = 0; j < NTOK; ++j) old[j] = (j < M) ? swap_old<EPI>(row, j, N, out, ldo) : 0.f;
 #pragma unroll
             for (int j = 0; j < NTOK; ++j)
-                if (j < M) swap_store<EPI>(acc[j], row, j, N, bias, out, ldo);
+                if (j < M) swap_store<EPI>(acc[j], old[j], row, j, N, bias, out, ldo);
         } else {
             // partial[split][token][row of this tile]; then the last CTA of the tile folds
             float* mine = partial + ((long long)(tile * splits + split) * NTOK) * 128 + quarter * 32 + lane;
@@ -385,15 +440,35 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (arrival == (unsigned)(splits - 1)) {
                 __threadfence();
                 const float* all = partial + ((long long)tile * splits * NTOK) * 128 + quarter * 32 + lane;
+                // four tokens and eight slabs at a time: 32 independent loads in flight, summed in
+                // slab order (adding the zeros of absent slabs changes nothing)
 #pragma unroll 1
-                for (int j = 0; j < M; ++j) {
-                    float v = 0.f;
-                    for (int s = 0; s < splits; ++s) v += __ldcg(all + ((long long)s * NTOK + j) * 128);
-                    swap_store<EPI>(v, row, j, N, bias, out, ldo);
+                for (int j0 = 0; j0 < M; j0 += 4) {
+                    float v[4] = {0.f, 0.f, 0.f, 0.f}, old[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) old[u] = (j0 + u < M) ? swap_old<EPI>(row, j0 + u, N, out, ldo) : 0.f;
+#pragma unroll 1
+                    for (int s0 = 0; s0 < splits; s0 += 8) {
+                        float t[4][8];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                t[u][q] = (j0 + u < M && s0 + q < splits)
+                                              ? __ldcg(all + ((long long)(s0 + q) * NTOK + j0 + u) * 128) : 0.f;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) v[u] += t[u][q];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (j0 + u < M) swap_store<EPI>(v[u], old[u], row, j0 + u, N, bias, out, ldo);
                 }
                 if (threadIdx.x == 64) counters[tile] = 0u;               // ready for the next launch
             }
         }
+        }   // R == 1
     }
     __syncthreads();
     if (warp == 1) {
@@ -502,21 +577,21 @@ AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void*
 }
 
 namespace axon {
-template <int NTOK, int STAGES>
+template <int NTOK, int STAGES, int R>
 static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* out,
                        float* partial, unsigned int* counters, int M, int N, int K, int ldo, int tiles, int splits,
                        int per_split, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (128 * TC_BK * 2 + NTOK * TC_BK * 2) + 1024;
+    constexpr size_t smem = (size_t)STAGES * (R * 128 * TC_BK * 2 + NTOK * TC_BK * 2) + 1024;
     const dim3 grid((unsigned)(tiles * splits)), block(192);
 #define AXON_SWAP_LAUNCH(E)                                                                                        \
     {                                                                                                              \
         static bool configured = false;                                                                            \
         if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<NTOK, STAGES, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<NTOK, STAGES, E, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("axon_gemm_tc_small: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
             configured = true;                                                                                     \
         }                                                                                                          \
-        launch_pdl(gemm_tc_swap_kernel<NTOK, STAGES, E>, grid, block, smem, stream, mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
+        launch_pdl(gemm_tc_swap_kernel<NTOK, STAGES, E, R>, grid, block, smem, stream, mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_SWAP_LAUNCH(TC_STORE_F32) break;
@@ -533,7 +608,9 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
 // The product for at most 64 activation rows (see gemm_tc_swap_kernel).  `partial` is
 // scratch for split-K partial tiles (`partial_floats` floats; 0 forbids splitting) and
 // `counters` an array of `n_counters` zeroed 32-bit counters that the kernel leaves zeroed.
-// Operands as in axon_gemm_tc.  Calls that share the scratch must not overlap on the GPU.
+// `target_ctas` is the number of CTAs to aim at (the SM count works best: one CTA per SM
+// leaves room for the next kernel's CTAs to preload their weights).  Operands as in
+// axon_gemm_tc.  Calls that share the scratch must not overlap on the GPU.
 AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias, void* out, int epilogue, int M,
                                 int N, int K, int ldo, float* partial, long long partial_floats,
                                 unsigned int* counters, int n_counters, int target_ctas, cudaStream_t stream) {
@@ -543,10 +620,15 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc_small: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc_small: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
     const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    const int tiles = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
-    // as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
+    const int tiles128 = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
+    // many rows: 256-row tiles halve the CTA count (no split then)
+    // (measured at 7B sizes: with 2 x target tiles, two 128-row CTAs per SM and six stages beat
+    // one 256-row CTA with three; the wide tile pays off only from several waves on)
+    const bool wide = ntok <= 32 && target_ctas > 0 && tiles128 >= 4 * target_ctas;
+    const int tiles = wide ? (N + 255) / 256 : tiles128;
+    // few rows: as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
     int splits = 1;
-    if (partial != nullptr && counters != nullptr && tiles <= n_counters && tiles < target_ctas) {
+    if (!wide && partial != nullptr && counters != nullptr && tiles <= n_counters && tiles < target_ctas) {
         splits = (target_ctas + tiles / 2) / tiles;
         if (splits > k_total / 4) splits = k_total / 4;
         const long long fit = partial_floats / ((long long)tiles * ntok * 128);
@@ -556,10 +638,12 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     const int per_split = (k_total + splits - 1) / splits;
     splits = (k_total + per_split - 1) / per_split;
     CUtensorMap mw, mx;
-    if (!tensor_map(w, N, K, 128, &mw) || !tensor_map(a, M, K, ntok, &mx)) return AXON_BAD_ARGUMENT;
-    if (ntok == 16) return launch_swap<16, 6>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
-    if (ntok == 32) return launch_swap<32, 5>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
-    return launch_swap<64, 4>(epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream);
+    if (!tensor_map(w, N, K, wide ? 256 : 128, &mw) || !tensor_map(a, M, K, ntok, &mx)) return AXON_BAD_ARGUMENT;
+#define AXON_SWAP_ARGS epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream
+    if (ntok == 16) return wide ? launch_swap<16, 3, 2>(AXON_SWAP_ARGS) : launch_swap<16, 6, 1>(AXON_SWAP_ARGS);
+    if (ntok == 32) return wide ? launch_swap<32, 3, 2>(AXON_SWAP_ARGS) : launch_swap<32, 5, 1>(AXON_SWAP_ARGS);
+    return launch_swap<64, 4, 1>(AXON_SWAP_ARGS);
+#undef AXON_SWAP_ARGS
 }
 
 // 0 when no kernel of this file ever gave up on a wait; else 1 + the role (0 producer,

@@ -7,6 +7,7 @@ checked here, before the launch, so a refusal never costs a failed launch.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -27,6 +28,12 @@ def _stream() -> int:
 
 
 _SPLIT_SCRATCH = {}
+#: how many CTAs a product for few rows aims at (K is cut into slabs until there are about
+#: this many): one per SM measured best, because the CTAs of the next kernel then fit beside them and preload their weights
+SPLIT_TARGET_CTAS = int(os.environ.get("AXON_SPLIT_TARGET_CTAS", 148))
+#: experiments: products with at most this many weight rows and at most 8 tokens take the
+#: mma.sync kernel instead of the swapped tcgen05 one (0 = never)
+MMA_SYNC_MAX_ROWS = int(os.environ.get("AXON_MMA_SYNC_MAX_ROWS", 0))
 
 
 def _split_scratch(device: torch.device):
@@ -34,7 +41,7 @@ def _split_scratch(device: torch.device):
     times 64 tokens times 128 rows) and zeroed tile counters that the kernel leaves zeroed."""
     got = _SPLIT_SCRATCH.get(device)
     if got is None:
-        got = (torch.empty(2 * 2 * SM_COUNT * 64 * 128, dtype=torch.float32, device=device),
+        got = (torch.empty(8 * SM_COUNT * 64 * 128, dtype=torch.float32, device=device),
                torch.zeros(1024, dtype=torch.int32, device=device))
         _SPLIT_SCRATCH[device] = got
     return got
@@ -42,12 +49,12 @@ def _split_scratch(device: torch.device):
 
 def _gemm_small(a, w, bias, out, epi, M, N, K) -> bool:
     """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one."""
-    if ENABLED["gemm_tc_small"]:
+    if ENABLED["gemm_tc_small"] and not (M <= 8 and N <= MMA_SYNC_MAX_ROWS):
         partial, counters = _split_scratch(a.device)
         check(lib.cuda().axon_gemm_tc_small(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                             out.data_ptr(), epi, M, N, K, out.stride(0), partial.data_ptr(),
-                                            partial.numel(), counters.data_ptr(), counters.numel(), 2 * SM_COUNT,
-                                            _stream()))
+                                            partial.numel(), counters.data_ptr(), counters.numel(),
+                                            SPLIT_TARGET_CTAS, _stream()))
         return True
     if ENABLED["gemm_small_m"]:
         check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),

@@ -327,7 +327,7 @@ def small_m_kernel(request):
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 23, 32, 33, 64])
 @pytest.mark.parametrize("N,K", [(16, 64), (2, 8), (33, 24), (1000, 160), (344, 344), (130, 1096), (4608, 3584),
-                                 (3584, 18944)])
+                                 (3584, 18944), (76032 + 6, 72)])
 def test_gemm_small_m(ops, small_m_kernel, M, N, K):
     from axon_b200.kernels import fast
     a = rand(M, K, dtype=torch.bfloat16, seed=70)
