@@ -9,8 +9,9 @@
 //  * decode: a CTA owns up to 16 query rows (one token's group of heads, or a few
 //    tokens') and a contiguous share ("split") of the key tiles; inside a tile each
 //    warp takes 16 of the 64 keys and the warps merge at the end.  With more than one
-//    split the CTA writes an unnormalised partial (o, m, l) to scratch and a second
-//    kernel folds the splits in ascending order.
+//    split the CTA writes an unnormalised partial (o, m, l) to scratch; the splits are
+//    folded in ascending order either by the CTA that finishes last (when the caller
+//    gives arrival counters) or by a second kernel.
 //
 // Keys and values are gathered row by row through the block table (any page size)
 // with 16-byte cp.async into a swizzled shared tile, double-buffered.  A row of a
@@ -34,6 +35,7 @@ struct FaParams {
     const int32_t* items;        // [n_items][2]: segment, first token of the tile within the segment
     float* part_o;               // [items][kv_heads][splits][16][hd]   (decode, splits > 1)
     float* part_ml;              // [items][kv_heads][splits][16][2]
+    unsigned int* counters;      // [items][kv_heads] arrivals of splits; zero before and after a launch
     PagedKv kv;
     int n_segments, heads, group, tokens_per_tile, n_splits, window;
     float scale_log2;            // scale * log2(e)
@@ -298,6 +300,67 @@ attention_fa_kernel(const FaParams p) {
             if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
         }
     }
+    if (p.n_splits == 1 || p.counters == nullptr) return;
+
+    // ---- the CTA that arrives last at this (item, kv head) folds the splits in ascending
+    // order and writes the output: no second kernel, and the partials are still in L2
+    __shared__ unsigned int arrival;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[item * gridDim.y + kvh], 1u);
+    __syncthreads();
+    if (arrival != (unsigned)(p.n_splits - 1)) return;
+    __threadfence();
+    float* wm = reinterpret_cast<float*>(smem_raw);      // [splits][16] maxima, then weights
+    float* wl = wm + FA_MAX_SPLITS * 16;                  // [splits][16] sums
+    const long long base0 = ((long long)item * gridDim.y + kvh) * p.n_splits * 16;
+    for (int e = threadIdx.x; e < p.n_splits * 16; e += FA_THREADS) {
+        wm[e] = __ldcg(p.part_ml + (base0 + e) * 2);
+        wl[e] = __ldcg(p.part_ml + (base0 + e) * 2 + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < rows_used) {
+        const int r = threadIdx.x;
+        float m = -INFINITY;
+        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, wm[s * 16 + r]);
+        const float use = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f;
+        for (int s = 0; s < p.n_splits; ++s) {
+            const float f = exp2f(wm[s * 16 + r] - use);
+            l += wl[s * 16 + r] * f;
+            wm[s * 16 + r] = f;
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        for (int s = 0; s < p.n_splits; ++s) wm[s * 16 + r] *= inv;
+    }
+    __syncthreads();
+    constexpr int EPT = (16 * HD + FA_THREADS - 1) / FA_THREADS;   // outputs per thread at most
+    float accv[EPT];
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) accv[k] = 0.f;
+    for (int s0 = 0; s0 < p.n_splits; s0 += 4) {
+        float tv[EPT][4];
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                tv[k][q] = (e < rows_used * HD && s0 + q < p.n_splits)
+                               ? __ldcg(p.part_o + (base0 + (s0 + q) * 16 + r) * HD + d) * wm[(s0 + q) * 16 + r] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < EPT; ++k)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) accv[k] += tv[k][q];
+    }
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
+        if (e >= rows_used * HD) continue;
+        const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+        p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(accv[k]);
+    }
+    if (threadIdx.x == 0) p.counters[item * gridDim.y + kvh] = 0u;    // ready for the next launch
 }
 
 // Fold the splits of each (item, kv head, row) in ascending order and normalise.
@@ -356,7 +419,7 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
     launch_pdl(attention_fa_kernel<HD, DECODE>, grid, dim3(FA_THREADS), smem, stream, p);
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
-    if (DECODE && p.n_splits > 1) {
+    if (DECODE && p.n_splits > 1 && p.counters == nullptr) {
         launch_pdl(attention_combine_kernel<HD>, dim3(n_items, kv_heads), dim3(128), 0, stream, p);
         st = launch_status("axon_attention_fa combine");
     }
@@ -380,12 +443,14 @@ AXON_API long long axon_attention_fa_scratch_floats(int n_items, int kv_heads, i
 }
 
 // decode != 0: tiles of 16 rows with `n_splits` key shares; else tiles of 64 rows.
+// `counters` (may be null): n_items * kv_heads zeroed 32-bit counters, left zeroed; with them
+// the split that finishes last folds the partials itself, without them a second kernel does.
 // tokens_per_tile * group rows must fit the tile.  scratch: see above (may be null when
 // n_splits == 1).  Head sizes 16, 32, 64, 128; group <= 16 (decode) or 64 (prefill).
 AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
                                const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
                                float scale, int window, int decode, int tokens_per_tile, int n_splits,
-                               float* scratch, cudaStream_t stream) {
+                               float* scratch, unsigned int* counters, cudaStream_t stream) {
     if (n_items <= 0) return AXON_OK;
     const int hd = layout->head_dim, kvh = layout->kv_heads;
     if (heads % kvh) { set_error("axon_attention_fa: %d heads over %d kv heads", heads, kvh); return AXON_BAD_ARGUMENT; }
@@ -399,6 +464,7 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
     p.segments = segments; p.items = items;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (long long)n_items * kvh * n_splits * 16 * hd : nullptr;
+    p.counters = (n_splits > 1) ? counters : nullptr;
     p.kv.block_table = layout->block_table; p.kv.table_stride = layout->table_stride; p.kv.page_size = layout->page_size;
     p.kv.kv_heads = kvh; p.kv.head_dim = hd; p.kv.page_stride = layout->page_stride;
     p.kv.entry_offset = layout->entry_offset; p.kv.v_offset = layout->v_offset;
@@ -424,10 +490,13 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
 // The split partials of one launch.  In host code this name is only a stand-in for
 // the symbol, not a device address: the address comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_fa_noalloc_scratch[AXON_FA_NOALLOC_SCRATCH_FLOATS];
+// Arrival counters of the splits (zero at load, and every launch leaves them zero).
+static __device__ __align__(256) unsigned int g_fa_noalloc_counters[AXON_FA_NOALLOC_COUNTERS];
 
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_fa_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device, once looked up
+unsigned int* g_fa_noalloc_counters_ptr[kMaxDevices] = {};
 }
 
 int axon_attention_fa_decode_noalloc(const void* q, const void* pool, void* out, const int32_t* segments,
@@ -457,8 +526,17 @@ int axon_attention_fa_decode_noalloc(const void* q, const void* pool, void* out,
             set_error("axon_attention_fa_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
             return AXON_CUDA_ERROR;
         }
+        unsigned int* cptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&cptr, g_fa_noalloc_counters);
+        if (e != cudaSuccess || cptr == nullptr) {
+            set_error("axon_attention_fa_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return AXON_CUDA_ERROR;
+        }
+        g_fa_noalloc_counters_ptr[dev] = cptr;
         g_fa_noalloc_ptr[dev] = ptr;
     }
     return axon_attention_fa(q, pool, out, segments, n_segments, items, n_items, layout, heads, scale, window,
-                             /*decode=*/1, tokens_per_tile, n_splits, g_fa_noalloc_ptr[dev], stream);
+                             /*decode=*/1, tokens_per_tile, n_splits, g_fa_noalloc_ptr[dev],
+                             (long long)n_items * layout->kv_heads <= AXON_FA_NOALLOC_COUNTERS ? g_fa_noalloc_counters_ptr[dev] : nullptr,
+                             stream);
 }

@@ -38,6 +38,9 @@
 #include <stdint.h>
 
 #define AXON_FA_NOALLOC_SCRATCH_FLOATS (4ll * 1024 * 1024)
+// arrival counters of the key splits, one per (item, kv head); launches with more items fold
+// their splits in a second kernel instead
+#define AXON_FA_NOALLOC_COUNTERS 4096
 
 struct AxonKvLayoutFa;
 

@@ -42,7 +42,8 @@ def _split_scratch(device: torch.device):
     got = _SPLIT_SCRATCH.get(device)
     if got is None:
         got = (torch.empty(8 * SM_COUNT * 64 * 128, dtype=torch.float32, device=device),
-               torch.zeros(1024, dtype=torch.int32, device=device))
+               torch.zeros(1024, dtype=torch.int32, device=device),      # tile counters of the products
+               torch.zeros(4096, dtype=torch.int32, device=device))      # split counters of attention
         _SPLIT_SCRATCH[device] = got
     return got
 
@@ -50,7 +51,7 @@ def _split_scratch(device: torch.device):
 def _gemm_small(a, w, bias, out, epi, M, N, K) -> bool:
     """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one."""
     if ENABLED["gemm_tc_small"] and not (M <= 8 and N <= MMA_SYNC_MAX_ROWS):
-        partial, counters = _split_scratch(a.device)
+        partial, counters, _ = _split_scratch(a.device)
         check(lib.cuda().axon_gemm_tc_small(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                             out.data_ptr(), epi, M, N, K, out.stride(0), partial.data_ptr(),
                                             partial.numel(), counters.data_ptr(), counters.numel(),
@@ -114,6 +115,12 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
 
 FA_HEAD_DIMS = (16, 32, 64, 128)
 FA_MAX_SPLITS = 32
+#: CTAs the decode attention aims at when it splits the keys of each request
+FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 2 * 148))
+#: whether the last split folds the partials itself (else a second kernel does; measured at 7B
+#: sizes the second kernel is a little faster up to batch 8 and equal at 64, because it overlaps
+#: with the kernels around it while the in-kernel fold lengthens the slowest CTA)
+FA_FOLD_IN_KERNEL = os.environ.get("AXON_FA_FOLD_IN_KERNEL", "0") != "0"
 SM_COUNT = 148
 
 
@@ -167,20 +174,25 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     n_seg = len(ctx.seg_slot)
     if it["n_dec"]:
         tiles = -(-it["dec_kv"] // 64)
-        splits = max(1, min(tiles, FA_MAX_SPLITS, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads))))
+        # small batches: about two CTAs per SM; large ones (a CTA per request and kv head fills
+        # the machine already) still gain from three or four shares of the keys
+        target = FA_TARGET_CTAS if it["n_dec"] * kv.kv_heads < SM_COUNT else 2 * FA_TARGET_CTAS
+        splits = max(1, min(tiles, FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads))))
         scratch = None
+        counters = _split_scratch(q.device)[2]
         if splits > 1:
             # sized for the most splits this batch can get, so that the buffer never moves
             # while the contexts grow (captured graphs hold its address)
-            most = min(FA_MAX_SPLITS, -(-2 * SM_COUNT // (it["n_dec"] * kv.kv_heads)))
+            most = min(FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads)))
             scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * most * 16 * (kv.head_dim + 2),),
                                     torch.float32)
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
                                    it["dec"].data_ptr(), it["n_dec"], kv._ref, heads, float(scale), int(kv.window),
                                    1, it["tpt_dec"], splits, None if scratch is None else scratch.data_ptr(),
+                                   counters.data_ptr() if FA_FOLD_IN_KERNEL and it["n_dec"] * kv.kv_heads <= counters.numel() else None,
                                    _stream()))
     if it["n_pre"]:
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
                                    it["pre"].data_ptr(), it["n_pre"], kv._ref, heads, float(scale), int(kv.window),
-                                   0, it["tpt_pre"], 1, None, _stream()))
+                                   0, it["tpt_pre"], 1, None, None, _stream()))
     return True

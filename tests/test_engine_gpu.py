@@ -300,6 +300,43 @@ def test_a_far_key_among_hundreds(tmp_path):
         check_rows(got, [want[-1], want[37], want[38]], TOL[dtype], f"far key, {dtype}, whole")
 
 
+def test_layer_sizes_of_the_large_model(tmp_path):
+    """One layer at the widths of the 7B configuration (hidden 3584, 28 heads over 4 kv
+    heads of 128, feed-forward 18944; the vocabulary is cut to 32003 so that the plain
+    float64 model fits in host memory): sizes at which the tuned kernels take their
+    multi-tile, split-K and multi-wave paths.  Whole, in portions, and decoded."""
+    from conftest import make_model_folder
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 1,
+           "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128,
+           "intermediate_size": 18944, "vocab_size": 32003, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+           "tie_word_embeddings": False, "max_position_embeddings": 512}
+    folder = make_model_folder(str(tmp_path / "wide"), cfg, 99, sharpen=4.0)
+    pcfg, w = plain.read_model(folder)
+    g = torch.Generator().manual_seed(5)
+    n = 150
+    toks = torch.randint(0, 32003, (n,), generator=g).tolist()
+    want = plain.forward(pcfg, w, toks)
+    del w
+    for dtype in ("float32", "bfloat16"):
+        engine = build(folder, dtype, max_tokens=512, page_size=16, max_positions=512, max_slots=2)
+        tr = Trace()
+        tr.step([("r", ("x",), toks, [0, 1, 63, 64, 127, 128, n - 1])], end=["r"])
+        got = replay(engine, tr.steps)[0]
+        check_rows(got, [want[i] for i in (0, 1, 63, 64, 127, 128, n - 1)], TOL[dtype], f"7B widths, {dtype}, whole")
+        tr, at = Trace(), 0
+        rows, pos = [], []
+        for size in (70, 2, 65, 1, 1, 1, 8, 1, 1):
+            tr.step([("r", ("x",), toks[at:at + size], [size - 1])], end=["r"] if at + size == n else [])
+            at += size
+            pos.append(at - 1)
+        assert at == n
+        got = replay(engine, tr.steps)
+        check_rows(torch.cat([got[k] for k in sorted(got)]), [want[p] for p in pos], TOL[dtype],
+                   f"7B widths, {dtype}, portions and decoded tokens")
+        del engine
+        torch.cuda.empty_cache()
+
+
 def test_step_refusals(model_folders):
     from axon_b200.engine.step import OutOfPages, StepEntry, StepError
     engine = build(model_folders["A"], "float32", max_tokens=32, page_size=16, max_slots=2)

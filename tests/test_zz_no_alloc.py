@@ -57,7 +57,7 @@ def _call(fn, view, q, segments, items, heads, hd, splits, scratch, out=None):
                 items.numel() // 2, view._ref, heads, scale, 0, 16 // group, splits, stream)
     else:
         rc = fn(q.data_ptr(), view.pool.data_ptr(), out.data_ptr(), segments.data_ptr(), n_seg, items.data_ptr(),
-                items.numel() // 2, view._ref, heads, scale, 0, 1, 16 // group, splits, scratch.data_ptr(), stream)
+                items.numel() // 2, view._ref, heads, scale, 0, 1, 16 // group, splits, scratch.data_ptr(), None, stream)
     torch.cuda.synchronize()
     return rc, out
 
