@@ -90,11 +90,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 enum { TC_STORE_F32 = 0, TC_STORE_BF16 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3 };
 
-template <int BN, int STAGES, int EPI>
+// RM: 128-row sub-tiles of activations per CTA (1 or 2).  With two, both MMAs of a k-step
+// read the same weight tile from shared memory, so a CTA needs 1.5x fewer operand bytes per
+// FLOP; the operand feed from L2, not the tensor pipe, bounds this kernel at prefill sizes.
+// BN: any multiple of 32 up to 256; RM * BN float columns of tensor memory hold the tile.
+template <int BN, int STAGES, int EPI, int RM>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int ldo, int m_tiles) {
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    constexpr uint32_t A_BYTES = RM * TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    constexpr uint32_t TMEM_COLS = RM * BN <= 32 ? 32 : RM * BN <= 64 ? 64 : RM * BN <= 128 ? 128 : RM * BN <= 256 ? 256 : 512;
     extern __shared__ unsigned char smem_dyn[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
@@ -105,7 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x % m_tiles, n_tile = blockIdx.x / m_tiles;
-    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
+    const int m0 = m_tile * TC_BM * RM, n0 = n_tile * BN;
     const int k_stages = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -113,9 +118,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(tmem_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {   // this warp owns tensor memory: BN float columns for the accumulator
+    if (warp == 1) {   // this warp owns tensor memory: RM * BN float columns for the accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+                     ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -149,8 +154,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint64_t da = smem_desc(sa), db = smem_desc(sw);
 #pragma unroll
                 for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
-                    // 16 elements = 32 bytes along K inside the swizzled row: +2 in the address field
-                    umma(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (ks | k) ? 1u : 0u);
+                    // 16 elements = 32 bytes along K inside the swizzled row: +2 in the address field;
+                    // sub-tile rm of the activations lies 16 KiB (+1024) further, its accumulator BN columns further
+#pragma unroll
+                    for (int rm = 0; rm < RM; ++rm)
+                        umma(tmem_acc + (uint32_t)(rm * BN), da + (uint64_t)(rm * 1024 + 2 * k), db + (uint64_t)(2 * k),
+                             idesc, (ks | k) ? 1u : 0u);
                 }
                 umma_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
             }
@@ -161,12 +170,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_wait(tmem_full, 0, 2);
         tc_fence_after();
         const int quarter = warp & 3;
-        const int m = m0 + quarter * 32 + lane;
         const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int cc = 0; cc < RM * (BN / 32); ++cc) {
+            const int rm = cc / (BN / 32), c = cc % (BN / 32);
+            const int m = m0 + rm * TC_BM + quarter * 32 + lane;
             uint32_t r[32];
-            tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
+            tmem_ld32(lane_addr + (uint32_t)(rm * BN + c * 32), r);
             const int nc = n0 + c * 32;
             if (m >= M || nc >= N) continue;
             if (EPI == TC_SWIGLU) {
@@ -249,7 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -530,21 +540,21 @@ static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtens
     return true;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int RM>
 static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M,
                      int N, int K, int ldo, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
-    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    constexpr size_t smem = (size_t)STAGES * (RM * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    const int m_tiles = (M + RM * TC_BM - 1) / (RM * TC_BM), n_tiles = (N + BN - 1) / BN;
     const dim3 grid((unsigned)(m_tiles * n_tiles)), block(192);
 #define AXON_TC_LAUNCH(E)                                                                                          \
     {                                                                                                              \
         static bool configured = false;                                                                            \
         if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("axon_gemm_tc: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
             configured = true;                                                                                     \
         }                                                                                                          \
-        gemm_tc_kernel<BN, STAGES, E><<<grid, block, smem, stream>>>(ma, mw, bias, out, M, N, K, ldo, m_tiles);    \
+        gemm_tc_kernel<BN, STAGES, E, RM><<<grid, block, smem, stream>>>(ma, mw, bias, out, M, N, K, ldo, m_tiles); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_TC_LAUNCH(TC_STORE_F32) break;
@@ -557,9 +567,37 @@ static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, cons
     return launch_status("axon_gemm_tc");
 }
 
+// The tile shape for a product: among (rows 128 or 256) x (columns 128, 192, 224, 256) the one
+// with the least modelled time.  The model: operand bytes all CTAs pull from L2
+// ((rows + columns) * K * 2 per tile) against what L2 delivers, and whole waves of tiles on 148
+// SMs against the tensor rate; it reproduces the measured 128 x 256 times within 5 %.
+struct TileShape { int rm, bn; };
+static TileShape choose_tile(int M, int N, int K) {
+    const int bns[4] = {256, 224, 192, 128};
+    TileShape best{1, 256};
+    double best_t = 1e30;
+    for (int rm = (M > TC_BM ? 2 : 1); rm >= 1; --rm) {
+        for (int bn : bns) {
+            const int rows = rm * TC_BM;
+            const long long tiles = (long long)((M + rows - 1) / rows) * ((N + bn - 1) / bn);
+            const double feed = (double)tiles * (rows + bn) * K * 2 / 12.9e12;
+            const double waves = (double)((tiles + 147) / 148);
+            const double compute = waves * (double)rows * bn * K * 2 / 15.2e12;
+            const double t = (feed > compute ? feed : compute) + 3e-6 * waves;
+            if (t < best_t * 0.98) { best_t = t; best = TileShape{rm, bn}; }
+        }
+    }
+    return best;
+}
+
 }  // namespace axon
 
 using namespace axon;
+
+// For tests and measurements: force the tile shape (rows 1 or 2 times 128; columns 128, 192,
+// 224 or 256); rm 0 gives the choice back to the model.
+static int g_force_rm = 0, g_force_bn = 0;
+AXON_API void axon_gemm_tc_force_tile(int rm, int bn) { g_force_rm = rm; g_force_bn = bn; }
 
 // a [M][K], w [N][K] bfloat16, contiguous, K % 8 == 0, 16-byte aligned.  Epilogues as in
 // axon_gemm_small_m: 0 float out, 1 bfloat16 out, 2 out += (float), 3 SwiGLU to bfloat16 [M][N/2].
@@ -569,11 +607,26 @@ AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void*
     if (K <= 0 || K % 8) { set_error("axon_gemm_tc: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
-    const bool wide = N > 128;
+    TileShape ts = choose_tile(M, N, K);
+    if (g_force_rm > 0) ts = TileShape{g_force_rm, g_force_bn};
     CUtensorMap ma, mw;
-    if (!tensor_map(a, M, K, TC_BM, &ma) || !tensor_map(w, N, K, wide ? 256 : 128, &mw)) return AXON_BAD_ARGUMENT;
-    if (wide) return launch_tc<256, 4>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
-    return launch_tc<128, 6>(epilogue, ma, mw, bias, out, M, N, K, ldo, stream);
+    if (!tensor_map(a, M, K, ts.rm * TC_BM, &ma) || !tensor_map(w, N, K, ts.bn, &mw)) return AXON_BAD_ARGUMENT;
+#define AXON_TC_ARGS epilogue, ma, mw, bias, out, M, N, K, ldo, stream
+    if (ts.rm == 2) {
+        switch (ts.bn) {
+            case 256: return launch_tc<256, 3, 2>(AXON_TC_ARGS);
+            case 224: return launch_tc<224, 3, 2>(AXON_TC_ARGS);
+            case 192: return launch_tc<192, 4, 2>(AXON_TC_ARGS);
+            default: return launch_tc<128, 4, 2>(AXON_TC_ARGS);
+        }
+    }
+    switch (ts.bn) {
+        case 256: return launch_tc<256, 4, 1>(AXON_TC_ARGS);
+        case 224: return launch_tc<224, 4, 1>(AXON_TC_ARGS);
+        case 192: return launch_tc<192, 5, 1>(AXON_TC_ARGS);
+        default: return launch_tc<128, 6, 1>(AXON_TC_ARGS);
+    }
+#undef AXON_TC_ARGS
 }
 
 namespace axon {

@@ -94,6 +94,8 @@ def cuda() -> ctypes.CDLL:
         lib.axon_last_error.argtypes = []
         lib.axon_topk_max.restype = c_int
         lib.axon_topk_max.argtypes = []
+        lib.axon_gemm_tc_force_tile.restype = None
+        lib.axon_gemm_tc_force_tile.argtypes = [c_int, c_int]
         for name, sig in list(_SIGNATURES.items()) + list(_OPTIONAL_SIGNATURES.items()):
             try:
                 _declare(lib, name, sig)

@@ -88,6 +88,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--target-ctas", type=int, default=0, help="gemm_small_m: CTAs the split-K aims at")
+    ap.add_argument("--tile", default="", help="gemm_tc: force the tile shape, e.g. 2x256 (rows/128 x columns)")
     ap.add_argument("--mma-sync", action="store_true", help="gemm_small_m: the mma.sync kernel, not the tcgen05 one")
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -108,6 +109,9 @@ def main() -> int:
             fn = lambda: fast.gemm(x, w, out, None, a.epilogue == "residual")
         if a.kernel == "gemm_tc" and a.m <= fast.SMALL_M:
             fast.ENABLED["gemm_small_m"] = fast.ENABLED["gemm_tc_small"] = False   # the 128-row-tile kernel
+        if a.tile:
+            rm, bn = a.tile.split("x")
+            lib.cuda().axon_gemm_tc_force_tile(int(rm), int(bn))
         if a.target_ctas:
             fast.SPLIT_TARGET_CTAS = a.target_ctas
         if a.mma_sync:

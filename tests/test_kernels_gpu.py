@@ -365,10 +365,23 @@ def test_gemm_small_m_refusals(ops):
     close(out, a.double() @ w.double().T, 2e-5)
 
 
-@pytest.mark.parametrize("M", [65, 128, 129, 300, 1100])
+@pytest.fixture(params=["auto", "1x256", "1x224", "1x192", "1x128", "2x256", "2x224", "2x192", "2x128"])
+def tile_shape(request):
+    """Every tile shape of the prefill product (rows / 128 x columns), and the model's own choice."""
+    from axon_b200.kernels import lib
+    if request.param == "auto":
+        lib.cuda().axon_gemm_tc_force_tile(0, 0)
+    else:
+        rm, bn = request.param.split("x")
+        lib.cuda().axon_gemm_tc_force_tile(int(rm), int(bn))
+    yield request.param
+    lib.cuda().axon_gemm_tc_force_tile(0, 0)
+
+
+@pytest.mark.parametrize("M", [65, 129, 300, 1100])
 @pytest.mark.parametrize("N,K", [(256, 64), (128, 8), (130, 72), (1000, 160), (344, 344), (2, 1096), (4608, 3584)])
-def test_gemm_tensor_core(ops, M, N, K):
-    """The tcgen05 kernel at sizes with tails in M, N and K, every epilogue."""
+def test_gemm_tensor_core(ops, tile_shape, M, N, K):
+    """The tcgen05 kernel at sizes with tails in M, N and K, every epilogue, every tile shape."""
     from axon_b200.kernels import fast
     a = rand(M, K, dtype=torch.bfloat16, seed=80)
     w = rand(N, K, dtype=torch.bfloat16, seed=81, std=0.1)
