@@ -14,7 +14,7 @@
 //    gives arrival counters) or by a second kernel.
 //
 // Keys and values are gathered row by row through the block table (any page size)
-// with 16-byte cp.async into a swizzled shared tile, double-buffered.  A row of a
+// with 16-byte cp.async into swizzled shared tiles, two (prefill) or three (decode) deep.  A row of a
 // tile is one key of one kv head (head_dim elements, contiguous in its page).
 // Scores are masked per element: key <= query position, and key > position - window
 // when a window is set, so the result does not depend on how the tokens were cut
@@ -75,19 +75,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Gather one 64-key tile of K or V (plane_off selects) for kv head `kvh` into shared memory.
+// Gather one 64-key tile of K and of V for kv head `kvh` into shared memory; a row's place
+// in its page is worked out once for both.
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(uint32_t smem_tile, const __nv_bfloat16* pool, const PagedKv& kv,
-                                             int slot, int kvh, int key0, int kv_len, long long plane_off) {
+__device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const __nv_bfloat16* pool,
+                                             const PagedKv& kv, int slot, int kvh, int key0, int kv_len) {
     constexpr int CPR = HD / 8;
     for (int e = threadIdx.x; e < FA_BN * CPR; e += FA_THREADS) {
         const int r = e / CPR, c = e % CPR;
         int pos = key0 + r;
         // rows past the request's length read its last position: finite data, masked later
         if (pos >= kv_len) pos = kv_len - 1;
-        const __nv_bfloat16* src = pool + kv.row(slot, pos, kvh) + plane_off + c * 8;
-        cp_async16(smem_tile + Swz<HD>::off(r, c), src);
+        const __nv_bfloat16* src = pool + kv.row(slot, pos, kvh) + c * 8;
+        const uint32_t off = Swz<HD>::off(r, c);
+        cp_async16(k_tile + off, src);
+        cp_async16(v_tile + off, src + kv.v_offset);
     }
+}
+template <int N> __device__ __forceinline__ void cp_async_wait_pending() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 template <int HD, bool DECODE>
@@ -98,18 +104,21 @@ attention_fa_kernel(const FaParams p) {
     constexpr int KSTEPS = HD / 16;           // k-steps of Q.K^T
     constexpr int NT_S = DECODE ? 2 : 8;      // 8-key score tiles per warp
     constexpr int NT_O = HD / 8;              // 8-dim output tiles
+    constexpr int NST = DECODE ? 3 : 2;       // K/V tiles in shared memory: NST - 1 in flight beside the current one
+    constexpr uint32_t TILE_BYTES = FA_BN * HD * 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();          // queries and this step's keys come from the kernels before
     const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t q_sm = smem;
     const uint32_t k_sm = q_sm + BM * HD * 2;
-    const uint32_t v_sm = k_sm + 2 * FA_BN * HD * 2;
+    const uint32_t v_sm = k_sm + NST * TILE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-    const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
+    // no work list: item i is the whole of segment i (steps of single tokens)
+    const int seg = p.items ? p.items[2 * item] : item, tok0 = p.items ? p.items[2 * item + 1] : 0;
     const int slot = p.segments[seg], q_start = p.segments[p.n_segments + seg];
     const int q_len = p.segments[2 * p.n_segments + seg], kv_len = p.segments[3 * p.n_segments + seg];
     const int ntok = min(p.tokens_per_tile, q_len - tok0);
@@ -132,11 +141,13 @@ attention_fa_kernel(const FaParams p) {
             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u));
         }
     }
-    if (t_begin < t_end) {
-        load_kv_tile<HD>(k_sm, p.pool, p.kv, slot, kvh, t_begin * FA_BN, kv_len, 0);
-        load_kv_tile<HD>(v_sm, p.pool, p.kv, slot, kvh, t_begin * FA_BN, kv_len, p.kv.v_offset);
+    // tiles t_begin .. t_begin + NST - 2 start now, one commit group each (the first also holds Q)
+#pragma unroll
+    for (int st = 0; st < NST - 1; ++st) {
+        if (t_begin + st < t_end)
+            load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, (t_begin + st) * FA_BN, kv_len);
+        cp_async_commit();
     }
-    cp_async_commit();
 
     // rows this thread holds: r_a = base + g, r_b = base + g + 8
     const int row_base = DECODE ? 0 : warp * 16;
@@ -153,14 +164,16 @@ attention_fa_kernel(const FaParams p) {
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     for (int tile = t_begin; tile < t_end; ++tile) {
-        const int buf = (tile - t_begin) & 1;
-        cp_async_wait_all();
-        __syncthreads();
-        if (tile + 1 < t_end) {
-            load_kv_tile<HD>(k_sm + (buf ^ 1) * FA_BN * HD * 2, p.pool, p.kv, slot, kvh, (tile + 1) * FA_BN, kv_len, 0);
-            load_kv_tile<HD>(v_sm + (buf ^ 1) * FA_BN * HD * 2, p.pool, p.kv, slot, kvh, (tile + 1) * FA_BN, kv_len, p.kv.v_offset);
+        const int buf = (tile - t_begin) % NST;
+        {
+            // the tile NST - 1 ahead goes into the buffer that the previous iteration finished with
+            const int ahead = tile + NST - 1, abuf = (ahead - t_begin) % NST;
+            if (ahead < t_end)
+                load_kv_tile<HD>(k_sm + abuf * TILE_BYTES, v_sm + abuf * TILE_BYTES, p.pool, p.kv, slot, kvh, ahead * FA_BN, kv_len);
+            cp_async_commit();
         }
-        cp_async_commit();
+        cp_async_wait_pending<NST - 1>();     // this tile's group (and every older one) has landed
+        __syncthreads();
         if (tile == t_begin) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -168,7 +181,7 @@ attention_fa_kernel(const FaParams p) {
                 ldsm_x4(q_sm + Swz<HD>::off(r, c), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
             }
         }
-        const uint32_t kt = k_sm + buf * FA_BN * HD * 2, vt = v_sm + buf * FA_BN * HD * 2;
+        const uint32_t kt = k_sm + buf * TILE_BYTES, vt = v_sm + buf * TILE_BYTES;
         const int key_base = DECODE ? warp * 16 : 0;   // first key (within the tile) of this warp
 
         // ---- S = Q K^T
@@ -237,6 +250,7 @@ attention_fa_kernel(const FaParams p) {
                 mma16816(o[2 * jp + 1], pf[kk], b2, b3);
             }
         }
+        __syncthreads();                      // everyone is done with this buffer before it is refilled
     }
     // the row sums live spread over the quad
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
@@ -369,7 +383,7 @@ __global__ void attention_combine_kernel(const FaParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int item = blockIdx.x, kvh = blockIdx.y;
-    const int seg = p.items[2 * item], tok0 = p.items[2 * item + 1];
+    const int seg = p.items ? p.items[2 * item] : item, tok0 = p.items ? p.items[2 * item + 1] : 0;
     const int q_start = p.segments[p.n_segments + seg], q_len = p.segments[2 * p.n_segments + seg];
     const int rows_used = min(p.tokens_per_tile, q_len - tok0) * p.group;
     // weight of each split for each row: 2^(m_s - m) / l, via shared memory
@@ -406,7 +420,7 @@ __global__ void attention_combine_kernel(const FaParams p) {
 template <int HD, bool DECODE>
 static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t stream) {
     constexpr int BM = DECODE ? 16 : 64;
-    constexpr size_t tiles = (size_t)BM * HD * 2 + 4 * (size_t)FA_BN * HD * 2;
+    constexpr size_t tiles = (size_t)BM * HD * 2 + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
     constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
     constexpr size_t smem = tiles > merge ? tiles : merge;
     static bool configured = false;

@@ -136,7 +136,8 @@ def _attention_items(ctx, group: int):
     if ctx.unit_items is not None:
         # single tokens only: the step brought its work list (segment, 0) along
         n = len(ctx.seg_q_len)
-        got = {"dec": ctx.unit_items if tpt_dec else None, "n_dec": n if tpt_dec else 0, "dec_kv": ctx.max_kv_len,
+        # (the decode shape takes "no list" to mean item i = segment i, which saves it a load)
+        got = {"dec": None, "n_dec": n if tpt_dec else 0, "dec_kv": ctx.max_kv_len,
                "pre": None if tpt_dec else ctx.unit_items, "n_pre": 0 if tpt_dec else n,
                "tpt_dec": tpt_dec, "tpt_pre": tpt_pre}
         ctx.scratch[key] = got
@@ -187,7 +188,8 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
             scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * most * 16 * (kv.head_dim + 2),),
                                     torch.float32)
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
-                                   it["dec"].data_ptr(), it["n_dec"], kv._ref, heads, float(scale), int(kv.window),
+                                   None if it["dec"] is None else it["dec"].data_ptr(), it["n_dec"], kv._ref, heads,
+                                   float(scale), int(kv.window),
                                    1, it["tpt_dec"], splits, None if scratch is None else scratch.data_ptr(),
                                    counters.data_ptr() if FA_FOLD_IN_KERNEL and it["n_dec"] * kv.kv_heads <= counters.numel() else None,
                                    _stream()))
