@@ -97,7 +97,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait_pending() {
 }
 
 template <int HD, bool DECODE>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, DECODE ? 1 : 3)     // prefill shape: three CTAs per SM
 attention_fa_kernel(const FaParams p) {
     constexpr int BM = DECODE ? 16 : 64;
     constexpr int CPR = HD / 8;
@@ -110,9 +110,11 @@ attention_fa_kernel(const FaParams p) {
     pdl_launch_dependents();
     pdl_wait();          // queries and this step's keys come from the kernels before
     const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
-    const uint32_t q_sm = smem;
-    const uint32_t k_sm = q_sm + BM * HD * 2;
+    // decode: [Q | K tiles | V tiles].  prefill: [K tiles | V tiles] with the queries parked in
+    // the last V tile until they are in registers (before that tile is first filled)
+    const uint32_t k_sm = DECODE ? smem + BM * HD * 2 : smem;
     const uint32_t v_sm = k_sm + NST * TILE_BYTES;
+    const uint32_t q_sm = DECODE ? smem : v_sm + (NST - 1) * TILE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -163,6 +165,17 @@ attention_fa_kernel(const FaParams p) {
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
+    if (!DECODE) {
+        // queries to registers now, so that their shared-memory tile can take keys' values
+        cp_async_wait_all();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int r = row_base + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
+            ldsm_x4(q_sm + Swz<HD>::off(r, c), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+        }
+        __syncthreads();
+    }
     for (int tile = t_begin; tile < t_end; ++tile) {
         const int buf = (tile - t_begin) % NST;
         {
@@ -174,7 +187,7 @@ attention_fa_kernel(const FaParams p) {
         }
         cp_async_wait_pending<NST - 1>();     // this tile's group (and every older one) has landed
         __syncthreads();
-        if (tile == t_begin) {
+        if (DECODE && tile == t_begin) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 const int r = row_base + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
@@ -420,7 +433,7 @@ __global__ void attention_combine_kernel(const FaParams p) {
 template <int HD, bool DECODE>
 static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t stream) {
     constexpr int BM = DECODE ? 16 : 64;
-    constexpr size_t tiles = (size_t)BM * HD * 2 + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
+    constexpr size_t tiles = (DECODE ? (size_t)BM * HD * 2 : 0) + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
     constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
     constexpr size_t smem = tiles > merge ? tiles : merge;
     static bool configured = false;

@@ -142,7 +142,7 @@ def _attention_items(ctx, group: int):
                "tpt_dec": tpt_dec, "tpt_pre": tpt_pre}
         ctx.scratch[key] = got
         return got
-    dec, pre = [], []
+    dec, pre, pre_work = [], [], []
     dec_kv = 0
     for s, (n, kv_len) in enumerate(zip(ctx.seg_q_len, ctx.seg_kv_len)):
         if tpt_dec and n <= tpt_dec:
@@ -150,7 +150,11 @@ def _attention_items(ctx, group: int):
             dec_kv = max(dec_kv, kv_len)
         else:
             for t0 in range(0, n, tpt_pre):
-                pre += [s, t0]
+                pre_work.append((kv_len - n + min(t0 + tpt_pre, n), s, t0))
+    # tiles with the most keys first: a causal tile's work grows with its position, and the
+    # long ones must not be the last to start
+    for _, s, t0 in sorted(pre_work, reverse=True):
+        pre += [s, t0]
     dev = ctx.tokens.device
     both = torch.tensor(dec + pre, dtype=torch.int32, device=dev) if dec or pre else None
     got = {"dec": both[:len(dec)] if dec else None, "n_dec": len(dec) // 2, "dec_kv": dec_kv,
