@@ -450,29 +450,33 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (arrival == (unsigned)(splits - 1)) {
                 __threadfence();
                 const float* all = partial + ((long long)tile * splits * NTOK) * 128 + quarter * 32 + lane;
-                // four tokens and eight slabs at a time: 32 independent loads in flight, summed in
-                // slab order (adding the zeros of absent slabs changes nothing)
+                // G tokens and four slabs at a time: up to 64 independent loads in flight per
+                // thread, summed in slab order (adding the zeros of absent slabs changes nothing)
+                constexpr int G = NTOK >= 32 ? 16 : 8;
 #pragma unroll 1
-                for (int j0 = 0; j0 < M; j0 += 4) {
-                    float v[4] = {0.f, 0.f, 0.f, 0.f}, old[4];
+                for (int j0 = 0; j0 < M; j0 += G) {
+                    float v[G], old[G];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) old[u] = (j0 + u < M) ? swap_old<EPI>(row, j0 + u, N, out, ldo) : 0.f;
+                    for (int u = 0; u < G; ++u) {
+                        v[u] = 0.f;
+                        old[u] = (j0 + u < M) ? swap_old<EPI>(row, j0 + u, N, out, ldo) : 0.f;
+                    }
 #pragma unroll 1
-                    for (int s0 = 0; s0 < splits; s0 += 8) {
-                        float t[4][8];
+                    for (int s0 = 0; s0 < splits; s0 += 4) {
+                        float t[G][4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                        for (int u = 0; u < G; ++u)
 #pragma unroll
-                            for (int q = 0; q < 8; ++q)
+                            for (int q = 0; q < 4; ++q)
                                 t[u][q] = (j0 + u < M && s0 + q < splits)
                                               ? __ldcg(all + ((long long)(s0 + q) * NTOK + j0 + u) * 128) : 0.f;
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                        for (int u = 0; u < G; ++u)
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) v[u] += t[u][q];
+                            for (int q = 0; q < 4; ++q) v[u] += t[u][q];
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
+                    for (int u = 0; u < G; ++u)
                         if (j0 + u < M) swap_store<EPI>(v[u], old[u], row, j0 + u, N, bias, out, ldo);
                 }
                 if (threadIdx.x == 64) counters[tile] = 0u;               // ready for the next launch
