@@ -13,81 +13,15 @@
 // Every wait on an mbarrier is bounded: when a wait gives up, the kernel records it in a
 // device flag (read with axon_gemm_tc_status) and carries on to its end, so tensor
 // memory is always freed and nothing spins forever.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#include <cuda.h>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
 
 namespace axon {
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_UMMA_K = 16;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;   // polls of try_wait before a wait gives up
-
-__device__ unsigned int g_tc_error = 0;        // 0 fine; else 1 + the role that gave up
-
-// ---- mbarrier / TMA / tcgen05 wrappers ------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Wait until the phase with this parity completes, at most TC_WAIT_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t role) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    atomicMax(&g_tc_error, 1u + role);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t smem, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major tile with 128-byte rows, 128-byte swizzle;
-// 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with a swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                            // 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
+constexpr int TC_BM = 128, TC_BK = 64;
 enum { TC_STORE_F32 = 0, TC_STORE_BF16 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3 };
 
 // RM: 128-row sub-tiles of activations per CTA (1 or 2).  With two, both MMAs of a k-step

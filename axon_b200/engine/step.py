@@ -102,9 +102,14 @@ class Engine:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot}: an entry needs at least one token")
-            for t in e.tokens:
-                if not (0 <= int(t) < vocab):
-                    raise StepError(f"slot {e.slot}: token {t} is outside the vocabulary of {vocab}")
+            if len(e.tokens) == 1:
+                bad = None if 0 <= int(e.tokens[0]) < vocab else e.tokens[0]
+            else:
+                toks = np.asarray(e.tokens)
+                out_of_range = (toks < 0) | (toks >= vocab)
+                bad = toks[out_of_range][0] if out_of_range.any() else None
+            if bad is not None:
+                raise StepError(f"slot {e.slot}: token {bad} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")

@@ -20,7 +20,7 @@ SMALL_M = 64
 
 #: switches for tests that compare a tuned kernel with the plain one
 ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attention_prefill": True,
-           "attention_decode": True}
+           "attention_decode": True, "attention_tc": True}
 
 
 def _stream() -> int:
@@ -99,6 +99,11 @@ def gemm_tc_status() -> int:
     return lib.cuda().axon_gemm_tc_status()
 
 
+def attention_tc_status() -> int:
+    """0 when no tensor-core attention ever gave up on a wait (synchronises the device)."""
+    return lib.cuda().axon_attention_tc_status()
+
+
 def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
     if not _bf16_operands(h, w_gate_up) or act.dtype != torch.bfloat16:
         return False
@@ -124,15 +129,15 @@ FA_FOLD_IN_KERNEL = os.environ.get("AXON_FA_FOLD_IN_KERNEL", "0") != "0"
 SM_COUNT = 148
 
 
-def _attention_items(ctx, group: int):
+def _attention_items(ctx, group: int, pre_rows: int = 64):
     """Work lists for the step's segments, cached per step and group size: segments that
     fit a 16-row tile (one or two decoded tokens) go to the decode shape, the others are
-    cut into tiles of up to 64 rows."""
-    key = ("fa_items", group)
+    cut into tiles of up to `pre_rows` rows."""
+    key = ("fa_items", group, pre_rows)
     got = ctx.scratch.get(key)
     if got is not None:
         return got
-    tpt_dec, tpt_pre = (16 // group if group <= 16 else 0), 64 // group
+    tpt_dec, tpt_pre = (16 // group if group <= 16 else 0), pre_rows // group
     if ctx.unit_items is not None:
         # single tokens only: the step brought its work list (segment, 0) along
         n = len(ctx.seg_q_len)
@@ -174,7 +179,9 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     if heads % kv.kv_heads or heads // kv.kv_heads > 64 or ctx.segments is None:
         return False
     group = heads // kv.kv_heads
-    it = _attention_items(ctx, group)
+    # prompt portions at head size 128 take the tcgen05 kernel with 128-row tiles
+    use_tc = ENABLED["attention_tc"] and kv.head_dim == 128 and ctx.unit_items is None
+    it = _attention_items(ctx, group, 128 if use_tc else 64)
     cu = lib.cuda()
     n_seg = len(ctx.seg_slot)
     if it["n_dec"]:
@@ -197,7 +204,11 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
                                    1, it["tpt_dec"], splits, None if scratch is None else scratch.data_ptr(),
                                    counters.data_ptr() if FA_FOLD_IN_KERNEL and it["n_dec"] * kv.kv_heads <= counters.numel() else None,
                                    _stream()))
-    if it["n_pre"]:
+    if it["n_pre"] and use_tc:
+        check(cu.axon_attention_tc(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
+                                   it["pre"].data_ptr(), it["n_pre"], kv._ref, heads, float(scale), int(kv.window),
+                                   it["tpt_pre"], _stream()))
+    elif it["n_pre"]:
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
                                    it["pre"].data_ptr(), it["n_pre"], kv._ref, heads, float(scale), int(kv.window),
                                    0, it["tpt_pre"], 1, None, None, _stream()))

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
+    "axon_attention_tc": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int, P],
+    "axon_attention_tc_status": [],
 }
 _OPTIONAL_SIGNATURES: dict = {}
 

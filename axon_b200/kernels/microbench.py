@@ -89,7 +89,7 @@ def main() -> int:
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--target-ctas", type=int, default=0, help="gemm_small_m: CTAs the split-K aims at")
     ap.add_argument("--tile", default="", help="gemm_tc: force the tile shape, e.g. 2x256 (rows/128 x columns)")
-    ap.add_argument("--mma-sync", action="store_true", help="gemm_small_m: the mma.sync kernel, not the tcgen05 one")
+    ap.add_argument("--mma-sync", action="store_true", help="gemm_small_m, attention_prefill: the mma.sync kernel, not the tcgen05 one")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         print("microbench needs a CUDA GPU", file=sys.stderr)
@@ -133,6 +133,8 @@ def main() -> int:
         q = torch.randn(ctx.n_tokens, a.heads * a.head_dim, generator=g, device=DEV).to(torch.bfloat16)
         out = torch.empty_like(q)
         scale = 1.0 / math.sqrt(a.head_dim)
+        if a.mma_sync:
+            fast.ENABLED["attention_tc"] = False
         fn = lambda: fast.attention(q, view, ctx, out, a.heads, scale)
         assert fn()
         us, best = _time(fn, a.iters, a.warmup, flush)
@@ -140,6 +142,7 @@ def main() -> int:
         nbytes = kv_bytes + 2 * q.numel() * 2
         pairs = a.batch * (a.context if decode else a.context * (a.context + 1) // 2)
         _report(a.kernel, a, us, best, nbytes, 4 * pairs * a.heads * a.head_dim)
+        assert fast.attention_tc_status() == 0
     else:
         x = torch.randn(a.m, a.k, generator=g, device=DEV)
         gain = torch.ones(a.k, device=DEV)

@@ -432,14 +432,16 @@ def _ctx_for(segs):
 @pytest.mark.parametrize("heads,kv_heads,hd,ps,window", [
     (4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (6, 2, 64, 8, 0), (28, 4, 128, 16, 0), (8, 8, 128, 16, 0),
     (40, 2, 64, 16, 0), (7, 1, 128, 1, 0), (6, 2, 64, 16, 70), (4, 2, 128, 16, 9)])
-@pytest.mark.parametrize("fold_in_kernel", [False, True])
-def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold_in_kernel, monkeypatch):
+@pytest.mark.parametrize("fold_in_kernel,tcgen05", [(False, True), (True, True), (False, False)])
+def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold_in_kernel, tcgen05, monkeypatch):
     """The tensor-core kernel on a mixed batch: decoded tokens at short and long contexts
     (one key; several splits), two-token portions, a whole prompt, a portion in the middle
     of a long request.  One key far back gets a large score so that a wrong page or a
     dropped tile shows."""
     from axon_b200.kernels import fast
     monkeypatch.setattr(fast, "FA_FOLD_IN_KERNEL", fold_in_kernel)   # both ways of folding the key splits
+    # prompt portions at head size 128: the tcgen05 kernel, or the mma.sync one as for other head sizes
+    monkeypatch.setitem(fast.ENABLED, "attention_tc", tcgen05)
     # (q_len, kv_len) per request
     shapes = [(1, 1), (1, 700), (2, 131), (100, 100), (37, 300), (1, 64), (1, 65), (3, 3)]
     max_pos = 704
@@ -479,6 +481,64 @@ def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold_in_ker
                 want = w @ vv
                 close(out[at + i].view(heads, hd)[h], want, 1.5e-2, f"request {s} token {i} head {h}")
                 close(plain_out[at + i].view(heads, hd)[h], want, 1e-2, f"plain kernel, request {s} token {i} head {h}")
+        at += n
+
+
+@pytest.mark.parametrize("heads,kv_heads,ps,window,shapes", [
+    (28, 4, 16, 0, [(600, 600), (300, 900), (129, 129)]),        # 126-row tiles, many key tiles
+    (12, 2, 8, 200, [(700, 700), (90, 1000)]),                   # a window: tiles wholly inside it, at its edges, before it
+    (3, 3, 32, 0, [(260, 260), (5, 400)]),                       # one head per kv head: 128 tokens a tile
+    (64, 1, 16, 0, [(70, 200)]),                                 # 64 heads to a kv head: two tokens a tile
+])
+def test_attention_tcgen05_prompts(ops, heads, kv_heads, ps, window, shapes):
+    """The tcgen05 kernel for prompt portions (head size 128) over several key tiles, against
+    float64.  One key far back gets a large score in one query of every request."""
+    from axon_b200.kernels import fast
+    hd = 128
+    max_pos = max(kv for _, kv in shapes)
+    slots = len(shapes)
+    view, table = make_cache(ops, torch.bfloat16, kv_heads, hd, ps, slots * -(-max_pos // ps), slots, max_pos,
+                             window=window, seed=21)
+    group = heads // kv_heads
+    ks, vs = [], []
+    for s, (n, kv_len) in enumerate(shapes):
+        k = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=500 + s)
+        v = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=600 + s)
+        ks.append(k); vs.append(v)
+        pages = table[s, : -(-kv_len // ps)].long()
+        pad = len(pages) * ps - kv_len
+        for which, t in ((0, k), (1, v)):
+            t = torch.cat([t, torch.zeros(pad, kv_heads, hd, dtype=t.dtype, device=DEV)])
+            view.pool[pages, view.entry, which] = t.view(len(pages), ps, kv_heads, hd).permute(0, 2, 1, 3)
+    ctx = _ctx_for([(s, n, kv_len) for s, (n, kv_len) in enumerate(shapes)])
+    q = rand(ctx.n_tokens, heads * hd, dtype=torch.bfloat16, seed=700)
+    qv = q.view(ctx.n_tokens, heads, hd)
+    at = 0
+    for s, (n, kv_len) in enumerate(shapes):
+        # the request's last query lines up with the oldest key it may still see
+        far = max(0, kv_len - window) if window else 3
+        for h in range(heads):
+            qv[at + n - 1, h] = (ks[s][far, h // group].float() * 1.5).to(torch.bfloat16)
+        at += n
+    out = torch.zeros_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    assert fast.ENABLED["attention_tc"]
+    assert fast.attention(q, view, ctx, out, heads, scale)
+    assert fast.attention_tc_status() == 0, "a wait inside the kernel gave up"
+    at = 0
+    for s, (n, kv_len) in enumerate(shapes):
+        qpos = torch.arange(kv_len - n, kv_len, device=DEV)[:, None]
+        kpos = torch.arange(kv_len, device=DEV)[None, :]
+        mask = kpos <= qpos
+        if window:
+            mask &= kpos > qpos - window
+        for h in range(heads):
+            sc = (qv[at:at + n, h].double() @ ks[s][:, h // group].double().T) * scale
+            w = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1)
+            if h == 0:
+                assert w[-1].max() > 0.5, "the planted key does not stand out"
+            close(out.view(-1, heads, hd)[at:at + n, h], w @ vs[s][:, h // group].double(), 1.5e-2,
+                  f"request {s} head {h}")
         at += n
 
 
