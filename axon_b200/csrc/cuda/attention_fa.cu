@@ -390,43 +390,86 @@ attention_fa_kernel(const FaParams p) {
     if (threadIdx.x == 0) p.counters[item * gridDim.y + kvh] = 0u;    // ready for the next launch
 }
 
-// Fold the splits of each (item, kv head, row) in ascending order and normalise.
+// Fold the splits of each (item, kv head, row) in ascending order and normalise.  A thread
+// owns float4s of the output; the partials of the first eight splits are requested before
+// the weights are known, so the kernel pays one round trip to memory (two beyond 8 splits).
+constexpr int FA_COMBINE_THREADS = 256;
 template <int HD>
-__global__ void attention_combine_kernel(const FaParams p) {
+__global__ void __launch_bounds__(FA_COMBINE_THREADS) attention_combine_kernel(const FaParams p) {
+    constexpr int V = HD / 4;                                            // float4s per row
+    constexpr int EPT = (16 * V + FA_COMBINE_THREADS - 1) / FA_COMBINE_THREADS;
+    constexpr int S = 8;                                                 // splits per batch of loads
     pdl_launch_dependents();
     pdl_wait();
     const int item = blockIdx.x, kvh = blockIdx.y;
     const int seg = p.items ? p.items[2 * item] : item, tok0 = p.items ? p.items[2 * item + 1] : 0;
     const int q_start = p.segments[p.n_segments + seg], q_len = p.segments[2 * p.n_segments + seg];
     const int rows_used = min(p.tokens_per_tile, q_len - tok0) * p.group;
-    // weight of each split for each row: 2^(m_s - m) / l, via shared memory
-    __shared__ float wgt[FA_MAX_SPLITS][16];
+    __shared__ float wm[FA_MAX_SPLITS * 16], wl[FA_MAX_SPLITS * 16];     // maxima (then weights) and sums of (split, row)
     const long long base0 = ((long long)item * gridDim.y + kvh) * p.n_splits * 16;
-    for (int e = threadIdx.x; e < p.n_splits * 16; e += blockDim.x)
-        wgt[e / 16][e % 16] = p.part_ml[(base0 + e) * 2];          // m_s of (split, row)
+    const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + base0;
+    const float4* po = reinterpret_cast<const float4*>(p.part_o) + base0 * V;   // [(split * 16 + row) * V + d4]
+    for (int e = threadIdx.x; e < p.n_splits * 16; e += FA_COMBINE_THREADS) {
+        const float2 v = __ldcg(ml + e);
+        wm[e] = v.x;
+        wl[e] = v.y;
+    }
+    float4 tv[EPT][S], acc[EPT];
+    auto load = [&](int s0) {
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_COMBINE_THREADS;
+#pragma unroll
+            for (int q = 0; q < S; ++q)
+                tv[k][q] = (e < rows_used * V && s0 + q < p.n_splits) ? __ldcg(po + (long long)(s0 + q) * 16 * V + e)
+                                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto fold = [&](int s0) {
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_COMBINE_THREADS, r = min(e / V, 15);
+#pragma unroll
+            for (int q = 0; q < S; ++q) {
+                const float w = s0 + q < p.n_splits ? wm[(s0 + q) * 16 + r] : 0.f;
+                acc[k].x += tv[k][q].x * w; acc[k].y += tv[k][q].y * w;
+                acc[k].z += tv[k][q].z * w; acc[k].w += tv[k][q].w * w;
+            }
+        }
+    };
+    load(0);
     __syncthreads();
     if (threadIdx.x < rows_used) {
         const int r = threadIdx.x;
         float m = -INFINITY;
-        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, wgt[s][r]);
+        for (int s = 0; s < p.n_splits; ++s) m = fmaxf(m, wm[s * 16 + r]);
         const float use = (m == -INFINITY) ? 0.f : m;
         float l = 0.f;
         for (int s = 0; s < p.n_splits; ++s) {
-            const float f = exp2f(wgt[s][r] - use);
-            l += p.part_ml[(base0 + s * 16 + r) * 2 + 1] * f;
-            wgt[s][r] = f;
+            const float f = exp2f(wm[s * 16 + r] - use);
+            l += wl[s * 16 + r] * f;
+            wm[s * 16 + r] = f;
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        for (int s = 0; s < p.n_splits; ++s) wgt[s][r] *= inv;
+        for (int s = 0; s < p.n_splits; ++s) wm[s * 16 + r] *= inv;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < rows_used * HD; e += blockDim.x) {
-        const int r = e / HD, d = e % HD;
-        float acc = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < p.n_splits; ++s) acc += p.part_o[(base0 + s * 16 + r) * HD + d] * wgt[s][r];
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    fold(0);
+    for (int s0 = S; s0 < p.n_splits; s0 += S) {
+        load(s0);
+        fold(s0);
+    }
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int e = threadIdx.x + k * FA_COMBINE_THREADS;
+        if (e >= rows_used * V) continue;
+        const int r = e / V, d = (e % V) * 4;
         const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
-        p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(acc);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[k].x, acc[k].y), hi = __floats2bfloat162_rn(acc[k].z, acc[k].w);
+        *reinterpret_cast<uint2*>(p.out + ((long long)tok * p.heads + head) * HD + d) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     }
 }
 
@@ -447,7 +490,7 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
     if (DECODE && p.n_splits > 1 && p.counters == nullptr) {
-        launch_pdl(attention_combine_kernel<HD>, dim3(n_items, kv_heads), dim3(128), 0, stream, p);
+        launch_pdl(attention_combine_kernel<HD>, dim3(n_items, kv_heads), dim3(FA_COMBINE_THREADS), 0, stream, p);
         st = launch_status("axon_attention_fa combine");
     }
     return st;

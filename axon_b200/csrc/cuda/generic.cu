@@ -60,6 +60,56 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     }
 }
 
+// The same for rows of whole float4s (dim % 4 == 0, aligned): a thread keeps its VPT float4s
+// of the row and of the gain in registers, so the row is read once and every load is in
+// flight before the first is used (the row's latency is paid once, not per element).
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(o) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int32_t* __restrict__ rows,
+                   TO* __restrict__ out, int dim, float eps, int unit_offset) {
+    __shared__ float red[32];
+    const int n4 = dim >> 2;
+    float4 g[VPT], v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {                // the gain does not depend on the kernel before
+        const int i = threadIdx.x + k * blockDim.x;
+        g[k] = i < n4 ? reinterpret_cast<const float4*>(gain)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long r_in = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + r_in * dim);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
+        ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    const float off = unit_offset ? 1.0f : 0.0f;
+    TO* o = out + (long long)blockIdx.x * dim;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4)
+            store4(o + 4 * i, v[k].x * inv * (off + g[k].x), v[k].y * inv * (off + g[k].y),
+                   v[k].z * inv * (off + g[k].z), v[k].w * inv * (off + g[k].w));
+    }
+}
+
 // ---------------------------------------------------------------------------
 // out[m][n] = sum_k a[m][k] * w[n][k] (+ bias[n]); mode 0 stores, mode 1 adds
 // into a float residual.  64x64 tile, 16-deep stages, 4x4 outputs per thread;
@@ -340,6 +390,20 @@ AXON_API int axon_rmsnorm(const float* x, const float* gain, const int32_t* rows
                           int out_dtype, int n_rows, int dim, float eps, int unit_offset,
                           cudaStream_t stream) {
     if (n_rows <= 0) return AXON_OK;
+    if (out_dtype != AXON_F32 && out_dtype != AXON_BF16) { set_error("axon_rmsnorm: unknown output dtype %d", out_dtype); return AXON_BAD_ARGUMENT; }
+    const int n4 = dim / 4;
+    if (dim % 4 == 0 && n4 <= 8 * 1024 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0) {
+        // whole float4s, at most 8 per thread: the kernel that reads the row once
+        int per = (n4 + 1023) / 1024;
+        per = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
+        int threads = ((n4 + per - 1) / per + 31) / 32 * 32;
+#define AXON_NORM_CASE(TO, VPT) launch_pdl(rmsnorm_vec_kernel<TO, VPT>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (TO*)out, dim, eps, unit_offset)
+#define AXON_NORM_TYPE(VPT) do { if (out_dtype == AXON_F32) AXON_NORM_CASE(float, VPT); else AXON_NORM_CASE(__nv_bfloat16, VPT); } while (0)
+        if (per == 1) AXON_NORM_TYPE(1); else if (per == 2) AXON_NORM_TYPE(2); else if (per == 4) AXON_NORM_TYPE(4); else AXON_NORM_TYPE(8);
+#undef AXON_NORM_TYPE
+#undef AXON_NORM_CASE
+        return launch_status("axon_rmsnorm");
+    }
     int threads = 128;
     while (threads < 1024 && threads * 4 < dim) threads *= 2;
     if (out_dtype == AXON_F32)

@@ -41,14 +41,41 @@ __device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v
 
 // best[r] = the id of the largest logit of row r (last index among equal maxima;
 // a NaN is picked only when the whole row is NaN, then the last index).
-__global__ void argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ best, int vocab,
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ best, int vocab,
                               long long row_stride) {
     __shared__ unsigned long long sm[32];
     pdl_launch_dependents();
     pdl_wait();
     const float* row = logits + (long long)blockIdx.x * row_stride;
     unsigned long long k = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    int tail = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        // whole float4s, eight loads in flight per thread: the row's latency is paid once per
+        // eight, not per element
+        const int n4 = vocab >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 8 * blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < n4 ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i >= n4) continue;
+                const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned long long c = key64(e[j], 4 * i + j);
+                    k = c > k ? c : k;
+                }
+            }
+        }
+        tail = n4 << 2;
+    }
+    for (int i = tail + threadIdx.x; i < vocab; i += blockDim.x) {
         const unsigned long long c = key64(row[i], i);
         k = c > k ? c : k;
     }

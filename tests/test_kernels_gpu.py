@@ -48,7 +48,8 @@ def test_embed(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("dim", [1, 50, 96, 1000, 3584 + 8])
+# whole float4s take the one-pass kernel with 1, 2, 4 or 8 of them per thread; the others the scalar one
+@pytest.mark.parametrize("dim", [1, 50, 96, 1000, 3584 + 8, 8192, 12288, 16400, 40000])
 def test_rmsnorm(ops, dtype, dim):
     x = rand(9, dim, seed=1, std=3.0)
     gain = rand(dim, seed=2) * 0.1 + 1.0
