@@ -5,10 +5,16 @@
 // a TMA producer thread copies 128 x 64 and BN x 64 element boxes (128-byte swizzle)
 // into a ring of shared-memory stages; one MMA thread issues tcgen05.mma (M 128, N BN,
 // K 16) four times per stage into a float accumulator in tensor memory and releases the
-// stage with tcgen05.commit; four epilogue warps read the accumulator back with
-// tcgen05.ld (a thread per output row) and apply the epilogue: store as float or
-// bfloat16 with an optional bias, add into a float residual, or SwiGLU over interleaved
-// gate/up columns.  Tails in M, N and K are zero-filled by TMA and masked at the store.
+// stage with tcgen05.commit; eight epilogue warps read the accumulator back with
+// tcgen05.ld (a thread per output row, two warps per 32 rows sharing the columns) and apply
+// the epilogue: store as float or bfloat16 with an optional bias, add into a float residual,
+// or SwiGLU over interleaved gate/up columns.  A warp stages its 32 rows x 32 columns in
+// shared memory (the ring is free by then) and hands them to TMA: a thread per row writing
+// straight to global memory touches 32 rows per store instruction, which made the epilogue
+// as long as half the K loop.  The residual is added by the TMA reduce (one add per element,
+// so the order is fixed).  Tails in M, N and K are zero-filled by TMA on the way in and
+// clipped on the way out; outputs that TMA cannot address (rows not 16-byte multiples) take
+// the stores from registers.
 //
 // Every wait on an mbarrier is bounded: when a wait gives up, the kernel records it in a
 // device flag (read with axon_gemm_tc_status) and carries on to its end, so tensor
@@ -28,9 +34,32 @@ enum { TC_STORE_F32 = 0, TC_STORE_BF16 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3 };
 // read the same weight tile from shared memory, so a CTA needs 1.5x fewer operand bytes per
 // FLOP; the operand feed from L2, not the tensor pipe, bounds this kernel at prefill sizes.
 // BN: any multiple of 32 up to 256; RM * BN float columns of tensor memory hold the tile.
-template <int BN, int STAGES, int EPI, int RM>
-__global__ void __launch_bounds__(192, 1)
+constexpr int TC_THREADS = 320;      // TMA warp, MMA warp, eight epilogue warps
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int BN, int STAGES, int EPI, int RM, bool TMA_OUT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_out,
                const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int ldo, int m_tiles) {
     constexpr uint32_t A_BYTES = RM * TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr uint32_t TMEM_COLS = RM * BN <= 32 ? 32 : RM * BN <= 64 ? 64 : RM * BN <= 128 ? 128 : RM * BN <= 256 ? 256 : 512;
@@ -100,13 +129,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             umma_commit(tmem_full);               // the accumulator is complete
         }
     } else {
-        // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ..
+        // ---- epilogue: warps 2..9; a warp reads tensor-memory lanes 32 * (warp % 4) .., and the
+        // two warps of a lane quarter take every other 32-column chunk
         mbar_wait(tmem_full, 0, 2);
+        __syncwarp();
         tc_fence_after();
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        if constexpr (TMA_OUT) {
+            // every MMA has read the ring and every load has landed: the ring is scratch now.
+            // Two 4 KiB buffers per warp: a chunk is staged while the one before is still being read out.
+            const uint32_t stage = smem_base + (uint32_t)(warp - 2) * 8192u;
+            int iter = 0;
 #pragma unroll 1
-        for (int cc = 0; cc < RM * (BN / 32); ++cc) {
+            for (int cc = half; cc < RM * (BN / 32); cc += 2) {
+                const int rm = cc / (BN / 32), c = cc % (BN / 32);
+                const int row0 = m0 + rm * TC_BM + quarter * 32, nc = n0 + c * 32;
+                if (row0 >= M || nc >= N) continue;               // the same for the whole warp
+                const uint32_t buf = stage + (uint32_t)(iter & 1) * 4096u;
+                if (iter >= 2) {
+                    if (lane == 0) bulk_wait_read<1>();           // the store that read this buffer is done with it
+                    __syncwarp();
+                }
+                uint32_t r[32];
+                tmem_ld32(lane_addr + (uint32_t)(rm * BN + c * 32), r);
+                if (bias) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (nc + i < N) r[i] = __float_as_uint(__uint_as_float(r[i]) + bias[nc + i]);
+                }
+                if (EPI == TC_SWIGLU) {
+                    // 16 outputs = 32 bytes per row; 32-byte swizzle: chunk bit 0 ^= row bit 2
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float g0 = __uint_as_float(r[4 * i]), u0 = __uint_as_float(r[4 * i + 1]);
+                        const float g1 = __uint_as_float(r[4 * i + 2]), u1 = __uint_as_float(r[4 * i + 3]);
+                        pk[i] = pack_bf16(__fdividef(g0, 1.0f + __expf(-g0)) * u0, __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        st_shared_v4(buf + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                } else if (EPI == TC_STORE_BF16) {
+                    // 32 outputs = 64 bytes per row; 64-byte swizzle: chunk bits 0..1 ^= row bits 1..2
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        st_shared_v4(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4),
+                                     pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                     pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                     pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                     pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                } else {
+                    // 32 floats = 128 bytes per row; 128-byte swizzle
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        st_shared_v4(buf + sw128_offset(lane, j), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = EPI == TC_SWIGLU ? (nc >> 1) : nc;
+                    if (EPI == TC_RESIDUAL) tma_reduce_add_2d(&map_out, buf, x, row0);
+                    else tma_store_2d(&map_out, buf, x, row0);
+                    bulk_commit();
+                }
+                ++iter;
+            }
+            if (lane == 0) bulk_wait_read<0>();                   // shared memory must outlive the reads
+        } else {
+#pragma unroll 1
+        for (int cc = half; cc < RM * (BN / 32); cc += 2) {
             const int rm = cc / (BN / 32), c = cc % (BN / 32);
             const int m = m0 + rm * TC_BM + quarter * 32 + lane;
             uint32_t r[32];
@@ -188,6 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
+        }   // !TMA_OUT
         tc_fence_before();
     }
     __syncthreads();
@@ -444,32 +537,42 @@ static EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+    const void* ptr; int rows, cols, box_rows, box_cols, ld, elem_bytes;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+               ld == o.ld && elem_bytes == o.elem_bytes;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows;
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.box_rows ^
+               ((size_t)k.box_cols << 20) ^ ((size_t)k.ld * 31u) ^ ((size_t)k.elem_bytes << 28);
     }
 };
 
-// A [rows][cols] bfloat16 row-major matrix seen as boxes of box_rows x 64 elements.
-static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+// A [rows][cols] row-major matrix (rows `ld` elements apart, bfloat16 or float) seen as boxes of
+// box_rows x box_cols elements, swizzled over the box's row bytes (32, 64 or 128).
+static bool tensor_map_any(const void* ptr, int rows, int cols, int ld, int elem_bytes, int box_rows, int box_cols,
+                           CUtensorMap* out) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    MapKey key{ptr, rows, cols, box_rows};
+    MapKey key{ptr, rows, cols, box_rows, box_cols, ld, elem_bytes};
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return true; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) { set_error("axon_gemm_tc: cuTensorMapEncodeTiled is not available from this driver"); return false; }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
+    const int row_bytes = box_cols * elem_bytes;
+    const CUtensorMapSwizzle swz = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = fn(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                    const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("axon_gemm_tc: cuTensorMapEncodeTiled failed with %d (rows %d cols %d)", (int)r, rows, cols); return false; }
     if (cache.size() > 4096) cache.clear();
@@ -477,22 +580,27 @@ static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtens
     *out = m;
     return true;
 }
+// An operand: [rows][cols] contiguous bfloat16 in boxes of box_rows x 64.
+static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    return tensor_map_any(ptr, rows, cols, cols, 2, box_rows, TC_BK, out);
+}
 
-template <int BN, int STAGES, int RM>
-static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, void* out, int M,
-                     int N, int K, int ldo, cudaStream_t stream) {
+template <int BN, int STAGES, int RM, bool TMA_OUT>
+static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const float* bias,
+                     void* out, int M, int N, int K, int ldo, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * (RM * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    static_assert(smem >= 8 * 8192 + 1024, "the epilogue stages its chunks in the ring");
     const int m_tiles = (M + RM * TC_BM - 1) / (RM * TC_BM), n_tiles = (N + BN - 1) / BN;
-    const dim3 grid((unsigned)(m_tiles * n_tiles)), block(192);
+    const dim3 grid((unsigned)(m_tiles * n_tiles)), block(TC_THREADS);
 #define AXON_TC_LAUNCH(E)                                                                                          \
     {                                                                                                              \
         static bool configured = false;                                                                            \
         if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("axon_gemm_tc: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
             configured = true;                                                                                     \
         }                                                                                                          \
-        gemm_tc_kernel<BN, STAGES, E, RM><<<grid, block, smem, stream>>>(ma, mw, bias, out, M, N, K, ldo, m_tiles); \
+        gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT><<<grid, block, smem, stream>>>(ma, mw, mo, bias, out, M, N, K, ldo, m_tiles); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_TC_LAUNCH(TC_STORE_F32) break;
@@ -534,8 +642,11 @@ using namespace axon;
 
 // For tests and measurements: force the tile shape (rows 1 or 2 times 128; columns 128, 192,
 // 224 or 256); rm 0 gives the choice back to the model.
-static int g_force_rm = 0, g_force_bn = 0;
+static int g_force_rm = 0, g_force_bn = 0, g_force_plain_out = 0;
 AXON_API void axon_gemm_tc_force_tile(int rm, int bn) { g_force_rm = rm; g_force_bn = bn; }
+// For tests: nonzero makes every output take the stores from registers, as outputs that TMA
+// cannot address do.
+AXON_API void axon_gemm_tc_force_plain_out(int on) { g_force_plain_out = on; }
 
 // a [M][K], w [N][K] bfloat16, contiguous, K % 8 == 0, 16-byte aligned.  Epilogues as in
 // axon_gemm_small_m: 0 float out, 1 bfloat16 out, 2 out += (float), 3 SwiGLU to bfloat16 [M][N/2].
@@ -547,23 +658,34 @@ AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void*
     if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
     TileShape ts = choose_tile(M, N, K);
     if (g_force_rm > 0) ts = TileShape{g_force_rm, g_force_bn};
-    CUtensorMap ma, mw;
+    CUtensorMap ma, mw, mo;
     if (!tensor_map(a, M, K, ts.rm * TC_BM, &ma) || !tensor_map(w, N, K, ts.bn, &mw)) return AXON_BAD_ARGUMENT;
-#define AXON_TC_ARGS epilogue, ma, mw, bias, out, M, N, K, ldo, stream
+    // the output through TMA when it can address it: 16-byte aligned base and rows (else from registers)
+    const int out_bytes = (epilogue == TC_STORE_BF16 || epilogue == TC_SWIGLU) ? 2 : 4;
+    const int out_cols = epilogue == TC_SWIGLU ? N / 2 : N;
+    const bool tma_out = !g_force_plain_out && ((uintptr_t)out & 15) == 0 && ((long long)ldo * out_bytes) % 16 == 0;
+    if (tma_out) {
+        if (!tensor_map_any(out, M, out_cols, ldo, out_bytes, 32, epilogue == TC_SWIGLU ? 16 : 32, &mo)) return AXON_BAD_ARGUMENT;
+    } else {
+        mo = ma;
+    }
+#define AXON_TC_ARGS epilogue, ma, mw, mo, bias, out, M, N, K, ldo, stream
+#define AXON_TC_SHAPE(BN, STAGES, RM) return tma_out ? launch_tc<BN, STAGES, RM, true>(AXON_TC_ARGS) : launch_tc<BN, STAGES, RM, false>(AXON_TC_ARGS)
     if (ts.rm == 2) {
         switch (ts.bn) {
-            case 256: return launch_tc<256, 3, 2>(AXON_TC_ARGS);
-            case 224: return launch_tc<224, 3, 2>(AXON_TC_ARGS);
-            case 192: return launch_tc<192, 4, 2>(AXON_TC_ARGS);
-            default: return launch_tc<128, 4, 2>(AXON_TC_ARGS);
+            case 256: AXON_TC_SHAPE(256, 3, 2);
+            case 224: AXON_TC_SHAPE(224, 3, 2);
+            case 192: AXON_TC_SHAPE(192, 4, 2);
+            default: AXON_TC_SHAPE(128, 4, 2);
         }
     }
     switch (ts.bn) {
-        case 256: return launch_tc<256, 4, 1>(AXON_TC_ARGS);
-        case 224: return launch_tc<224, 4, 1>(AXON_TC_ARGS);
-        case 192: return launch_tc<192, 5, 1>(AXON_TC_ARGS);
-        default: return launch_tc<128, 6, 1>(AXON_TC_ARGS);
+        case 256: AXON_TC_SHAPE(256, 4, 1);
+        case 224: AXON_TC_SHAPE(224, 4, 1);
+        case 192: AXON_TC_SHAPE(192, 5, 1);
+        default: AXON_TC_SHAPE(128, 6, 1);
     }
+#undef AXON_TC_SHAPE
 #undef AXON_TC_ARGS
 }
 

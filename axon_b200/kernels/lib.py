@@ -98,6 +98,8 @@ def cuda() -> ctypes.CDLL:
         lib.axon_topk_max.argtypes = []
         lib.axon_gemm_tc_force_tile.restype = None
         lib.axon_gemm_tc_force_tile.argtypes = [c_int, c_int]
+        lib.axon_gemm_tc_force_plain_out.restype = None
+        lib.axon_gemm_tc_force_plain_out.argtypes = [c_int]
         for name, sig in list(_SIGNATURES.items()) + list(_OPTIONAL_SIGNATURES.items()):
             try:
                 _declare(lib, name, sig)

@@ -413,6 +413,44 @@ def test_gemm_tensor_core(ops, tile_shape, M, N, K):
     assert fast.gemm_tc_status() == 0, "a wait inside the kernel gave up"
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 1024, 160), (1100, 4608, 512)])
+def test_gemm_tensor_core_output_paths(ops, M, N, K):
+    """Outputs that TMA can address leave through shared memory and TMA (clipped at the edges, the
+    residual by TMA's add); the others are stored from registers.  Both give the same numbers."""
+    from axon_b200.kernels import fast, lib
+    a = rand(M, K, dtype=torch.bfloat16, seed=90)
+    w = rand(N, K, dtype=torch.bfloat16, seed=91, std=0.1)
+    bias = rand(N, seed=92)
+    res = rand(M, N, seed=93)
+    got = {}
+    try:
+        for plain in (0, 1):
+            lib.cuda().axon_gemm_tc_force_plain_out(plain)
+            f32 = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+            bf = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+            acc = res.clone()
+            act = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+            assert fast.gemm(a, w, f32, bias, False) and fast.gemm(a, w, bf, bias, False)
+            assert fast.gemm(a, w, acc, None, True) and fast.gemm_swiglu(a, w, act)
+            # a window into a wider buffer: rows further apart than they are long, edges must stay untouched
+            wide = torch.full((M + 2, N + 8), 5.0, dtype=torch.float32, device=DEV)
+            assert fast.gemm(a, w, wide[1:M + 1, 4:N + 4], None, False)
+            got[plain] = (f32, bf, acc, act, wide)
+    finally:
+        lib.cuda().axon_gemm_tc_force_plain_out(0)
+    want = a.double() @ w.double().T
+    close(got[0][0], want + bias.double(), 2e-5, "float output through TMA")
+    close(got[0][2], want + res.double(), 2e-5, "residual through TMA's add")
+    g, u = want[:, 0::2], want[:, 1::2]
+    close(got[0][3], g / (1 + torch.exp(-g)) * u, OUT_TOL[torch.bfloat16], "SwiGLU through TMA")
+    for x, y, name in zip(got[0], got[1], ("float", "bfloat16", "residual", "SwiGLU", "window")):
+        close(x, y.double(), 1e-6 if x.dtype == torch.float32 else 8e-3, f"{name}: TMA against registers")
+    wide = got[0][4]
+    close(wide[1:M + 1, 4:N + 4], want, 2e-5, "window")
+    assert (wide[0] == 5).all() and (wide[-1] == 5).all() and (wide[:, :4] == 5).all() and (wide[:, -4:] == 5).all()
+    assert fast.gemm_tc_status() == 0
+
+
 def _ctx_for(segs):
     """A StepContext for segments [(slot, q_len, kv_len)] with tokens flattened in order."""
     from axon_b200.parts import Runtime, StepContext
