@@ -108,7 +108,11 @@ attention_fa_kernel(const FaParams p) {
     constexpr uint32_t TILE_BYTES = FA_BN * HD * 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     pdl_launch_dependents();
-    pdl_wait();          // queries and this step's keys come from the kernels before
+    // The prompt shape waits here: queries and this step's keys come from the kernels before.
+    // The decode shape first requests the key tiles that hold only older positions (nothing in
+    // this step writes them; lengths and block tables are in place before the step starts), so
+    // that the cache streams in while the kernels before are still finishing.
+    if (!DECODE) pdl_wait();
     const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
     // decode: [Q | K tiles | V tiles].  prefill: [K tiles | V tiles] with the queries parked in
     // the last V tile until they are in registers (before that tile is first filled)
@@ -132,6 +136,17 @@ attention_fa_kernel(const FaParams p) {
     const int per = (tile_hi - tile_lo + p.n_splits - 1) / p.n_splits;
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi, t_begin + per);
 
+    const int new_from = kv_len - q_len;              // the segment's first position written by this step
+    if (DECODE) {
+#pragma unroll
+        for (int st = 0; st < NST - 1; ++st) {
+            const int tile = t_begin + st;
+            if (tile < t_end && (tile + 1) * FA_BN <= new_from)
+                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
+            cp_async_commit();
+        }
+        pdl_wait();
+    }
     // ---- Q tile -> shared (rows beyond rows_used are zero)
     for (int e = threadIdx.x; e < BM * CPR; e += FA_THREADS) {
         const int r = e / CPR, c = e % CPR;
@@ -143,12 +158,24 @@ attention_fa_kernel(const FaParams p) {
             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u));
         }
     }
-    // tiles t_begin .. t_begin + NST - 2 start now, one commit group each (the first also holds Q)
+    if (DECODE) {
+        // the tiles of the first NST - 1 that hold new positions, in one group with the queries
+        // (the first round waits for every group)
 #pragma unroll
-    for (int st = 0; st < NST - 1; ++st) {
-        if (t_begin + st < t_end)
-            load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, (t_begin + st) * FA_BN, kv_len);
+        for (int st = 0; st < NST - 1; ++st) {
+            const int tile = t_begin + st;
+            if (tile < t_end && (tile + 1) * FA_BN > new_from)
+                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
+        }
         cp_async_commit();
+    } else {
+        // tiles t_begin .. t_begin + NST - 2 start now, one commit group each (the first also holds Q)
+#pragma unroll
+        for (int st = 0; st < NST - 1; ++st) {
+            if (t_begin + st < t_end)
+                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, (t_begin + st) * FA_BN, kv_len);
+            cp_async_commit();
+        }
     }
 
     // rows this thread holds: r_a = base + g, r_b = base + g + 8
@@ -185,7 +212,8 @@ attention_fa_kernel(const FaParams p) {
                 load_kv_tile<HD>(k_sm + abuf * TILE_BYTES, v_sm + abuf * TILE_BYTES, p.pool, p.kv, slot, kvh, ahead * FA_BN, kv_len);
             cp_async_commit();
         }
-        cp_async_wait_pending<NST - 1>();     // this tile's group (and every older one) has landed
+        if (DECODE && tile == t_begin) cp_async_wait_all();   // queries included
+        else cp_async_wait_pending<NST - 1>();                // this tile's group (and every older one) has landed
         __syncthreads();
         if (DECODE && tile == t_begin) {
 #pragma unroll

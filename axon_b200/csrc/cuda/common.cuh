@@ -70,6 +70,55 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
     return r;
 }
 
+// Partial products that a split-K product for few rows left in scratch for the kernel that
+// reads its output: partial[((n / 128) * splits + s) * ntok + token][n % 128] holds slab s of
+// output (token, n).  The reader adds the slabs in ascending order (so the sum does not
+// depend on timing), then the bias; `partial == nullptr` means there is nothing to fold.
+struct SplitFold {
+    const float* partial;
+    const float* bias;
+    int splits, ntok;
+
+    __device__ __forceinline__ float at(int token, int n) const {
+        const float* p = partial + ((long long)(n >> 7) * splits * ntok + token) * 128 + (n & 127);
+        const long long step = (long long)ntok * 128;
+        float v = 0.f;
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float t0 = __ldcg(p + s * step), t1 = __ldcg(p + (s + 1) * step);
+            const float t2 = __ldcg(p + (s + 2) * step), t3 = __ldcg(p + (s + 3) * step);
+            v += t0; v += t1; v += t2; v += t3;
+        }
+        for (; s < splits; ++s) v += __ldcg(p + s * step);
+        if (bias) v += bias[n];
+        return v;
+    }
+    // four consecutive outputs n .. n + 3 (n % 4 == 0, so they lie in one 128-row tile)
+    __device__ __forceinline__ float4 at4(int token, int n) const {
+        const float4* p = reinterpret_cast<const float4*>(partial + ((long long)(n >> 7) * splits * ntok + token) * 128 + (n & 127));
+        const long long step = (long long)ntok * 32;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float4 t0 = __ldcg(p + s * step), t1 = __ldcg(p + (s + 1) * step);
+            const float4 t2 = __ldcg(p + (s + 2) * step), t3 = __ldcg(p + (s + 3) * step);
+            v.x += t0.x; v.y += t0.y; v.z += t0.z; v.w += t0.w;
+            v.x += t1.x; v.y += t1.y; v.z += t1.z; v.w += t1.w;
+            v.x += t2.x; v.y += t2.y; v.z += t2.z; v.w += t2.w;
+            v.x += t3.x; v.y += t3.y; v.z += t3.z; v.w += t3.w;
+        }
+        for (; s < splits; ++s) {
+            const float4 t = __ldcg(p + s * step);
+            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        }
+        if (bias) {
+            const float4 b = *reinterpret_cast<const float4*>(bias + n);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        return v;
+    }
+};
+
 // Where position `pos` of the request in `slot` lies: the element offset of row
 // (kv_head, pos % page_size) of its page within one layer's K (or V) plane.
 // Cache layout: pool[page][entry][2: K,V][kv_head][page_size][head_dim].

@@ -298,7 +298,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // when a matrix has few 128-row tiles, K is cut into `splits` slabs, one CTA each: every
 // CTA writes its partial tile to scratch, and the CTA that arrives last at the tile's
 // counter adds the partials in slab order (so the sum does not depend on timing) and
-// applies the epilogue.  In tensor memory a lane is a weight row and a column a token,
+// applies the epilogue.  Without counters the partial tiles are the result: the kernel
+// that reads the output next (a norm, the rotation) adds them on its way (SplitFold), which
+// takes the fence, the counter and the gathering pass off this kernel's tail.  In tensor memory a lane is a weight row and a column a token,
 // so for a fixed token the 32 lanes of a warp write 32 consecutive outputs.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -470,6 +472,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int j = 0; j < NTOK; ++j)
                 if (j < M) mine[j * 128] = acc[j];
+            if (counters != nullptr) {
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps
             if (threadIdx.x == 64) arrival = atomicAdd(&counters[tile], 1u);
@@ -508,6 +511,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
                 if (threadIdx.x == 64) counters[tile] = 0u;               // ready for the next launch
             }
+            }   // counters: this kernel folds
         }
         }   // R == 1
     }
@@ -724,9 +728,15 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
 // `target_ctas` is the number of CTAs to aim at (the SM count works best: one CTA per SM
 // leaves room for the next kernel's CTAs to preload their weights).  Operands as in
 // axon_gemm_tc.  Calls that share the scratch must not overlap on the GPU.
+// `defer` (store-float and residual epilogues): when the product is split, leave the partial
+// sums in `partial` for the reader of the output (SplitFold: axon_rmsnorm_fold,
+// axon_rope_kv_write, axon_fold_partials), which must run before `partial` is written again;
+// bias and residual are then the reader's to add and `out` is not touched.
+// `plan` (may be null) receives {splits, token columns of the partial tiles, deferred 0/1}.
 AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias, void* out, int epilogue, int M,
                                 int N, int K, int ldo, float* partial, long long partial_floats,
-                                unsigned int* counters, int n_counters, int target_ctas, cudaStream_t stream) {
+                                unsigned int* counters, int n_counters, int target_ctas, int defer, int* plan,
+                                cudaStream_t stream) {
     if (M <= 0 || N <= 0) return AXON_OK;
     if (M > 64) { set_error("axon_gemm_tc_small: %d rows; this kernel takes at most 64", M); return AXON_BAD_ARGUMENT; }
     if (K <= 0 || K % 8) { set_error("axon_gemm_tc_small: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
@@ -750,6 +760,9 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     }
     const int per_split = (k_total + splits - 1) / splits;
     splits = (k_total + per_split - 1) / per_split;
+    const bool deferred = defer && splits > 1 && (epilogue == TC_STORE_F32 || epilogue == TC_RESIDUAL);
+    if (plan) { plan[0] = splits; plan[1] = ntok; plan[2] = deferred ? 1 : 0; }
+    if (deferred) counters = nullptr;                 // the kernel stops after writing its partial tile
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, wide ? 256 : 128, &mw) || !tensor_map(a, M, K, ntok, &mx)) return AXON_BAD_ARGUMENT;
 #define AXON_SWAP_ARGS epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream

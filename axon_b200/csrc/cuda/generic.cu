@@ -37,18 +37,24 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __rest
 // ---------------------------------------------------------------------------
 // RMSNorm: h = x * rsqrt(mean(x^2) + eps) * gain, one block per row.
 // `rows` (optional) gathers: output row r is the norm of input row rows[r].
+// With `fold` the row first takes the partial products that the product before left for it
+// (x[row] += sum of the slabs, written back), so that product needs no pass of its own to add them.
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+__global__ void rmsnorm_kernel(float* x, const float* __restrict__ gain,
                                const int32_t* __restrict__ rows, TO* __restrict__ out, int dim,
-                               float eps, int unit_offset) {
+                               float eps, int unit_offset, SplitFold fold) {
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
     const long long r_in = rows ? rows[blockIdx.x] : blockIdx.x;
-    const float* xr = x + r_in * dim;
+    float* xr = x + r_in * dim;
     float ss = 0.f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        const float v = xr[d];
+        float v = xr[d];
+        if (fold.partial) {
+            v += fold.at((int)r_in, d);
+            xr[d] = v;                             // read again below by the same thread
+        }
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, red);
@@ -72,8 +78,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float
 }
 template <typename TO, int VPT>
 __global__ void __launch_bounds__(1024)
-rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int32_t* __restrict__ rows,
-                   TO* __restrict__ out, int dim, float eps, int unit_offset) {
+rmsnorm_vec_kernel(float* x, const float* __restrict__ gain, const int32_t* __restrict__ rows,
+                   TO* __restrict__ out, int dim, float eps, int unit_offset, SplitFold fold) {
     __shared__ float red[32];
     const int n4 = dim >> 2;
     float4 g[VPT], v[VPT];
@@ -85,11 +91,22 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain, 
     pdl_launch_dependents();
     pdl_wait();
     const long long r_in = rows ? rows[blockIdx.x] : blockIdx.x;
-    const float4* xr = reinterpret_cast<const float4*>(x + r_in * dim);
+    float4* xr = reinterpret_cast<float4*>(x + r_in * dim);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
         v[k] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (fold.partial) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) {
+                const float4 f = fold.at4((int)r_in, 4 * i);
+                v[k].x += f.x; v[k].y += f.y; v[k].z += f.z; v[k].w += f.w;
+                xr[i] = v[k];
+            }
+        }
     }
     float ss = 0.f;
 #pragma unroll
@@ -211,7 +228,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
                                      const int32_t* __restrict__ positions,
                                      const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
                                      T* __restrict__ pool, PagedKv kv, int heads, int rot, int adjacent,
-                                     int write_kv) {
+                                     int write_kv, SplitFold fold) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -236,7 +253,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
             ia = base + 2 * j; ib = base + 2 * j + 1;
         }
         if (h < heads) {
-            const float a = row[h * hd + ia], b = row[h * hd + ib];
+            const float a = fold.partial ? fold.at(t, h * hd + ia) : row[h * hd + ia];
+            const float b = fold.partial ? fold.at(t, h * hd + ib) : row[h * hd + ib];
             float ra = a, rb = b;
             if (rotate) {
                 const float2 cs = table[(long long)t * rhalf + i];
@@ -248,8 +266,9 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
         } else if (write_kv) {
             const bool is_v = h >= heads + kv.kv_heads;
             const int kh = is_v ? h - heads - kv.kv_heads : h - heads;
-            const float* src = row + q_dim + (is_v ? kv_dim : 0) + kh * hd;
-            const float a = src[ia], b = src[ib];
+            const int col = q_dim + (is_v ? kv_dim : 0) + kh * hd;
+            const float a = fold.partial ? fold.at(t, col + ia) : row[col + ia];
+            const float b = fold.partial ? fold.at(t, col + ib) : row[col + ib];
             float ra = a, rb = b;
             if (rotate && !is_v) {
                 const float2 cs = table[(long long)t * rhalf + i];
@@ -386,18 +405,18 @@ AXON_API int axon_embed(const int32_t* tokens, const void* table, int table_dtyp
     return launch_status("axon_embed");
 }
 
-AXON_API int axon_rmsnorm(const float* x, const float* gain, const int32_t* rows, void* out,
-                          int out_dtype, int n_rows, int dim, float eps, int unit_offset,
-                          cudaStream_t stream) {
+static int rmsnorm_launch(float* x, const float* gain, const int32_t* rows, void* out, int out_dtype, int n_rows,
+                          int dim, float eps, int unit_offset, SplitFold fold, cudaStream_t stream) {
     if (n_rows <= 0) return AXON_OK;
     if (out_dtype != AXON_F32 && out_dtype != AXON_BF16) { set_error("axon_rmsnorm: unknown output dtype %d", out_dtype); return AXON_BAD_ARGUMENT; }
     const int n4 = dim / 4;
-    if (dim % 4 == 0 && n4 <= 8 * 1024 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0) {
+    if (dim % 4 == 0 && n4 <= 8 * 1024 &&
+        (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)fold.partial | (uintptr_t)fold.bias) & 15) == 0) {
         // whole float4s, at most 8 per thread: the kernel that reads the row once
         int per = (n4 + 1023) / 1024;
         per = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
         int threads = ((n4 + per - 1) / per + 31) / 32 * 32;
-#define AXON_NORM_CASE(TO, VPT) launch_pdl(rmsnorm_vec_kernel<TO, VPT>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (TO*)out, dim, eps, unit_offset)
+#define AXON_NORM_CASE(TO, VPT) launch_pdl(rmsnorm_vec_kernel<TO, VPT>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (TO*)out, dim, eps, unit_offset, fold)
 #define AXON_NORM_TYPE(VPT) do { if (out_dtype == AXON_F32) AXON_NORM_CASE(float, VPT); else AXON_NORM_CASE(__nv_bfloat16, VPT); } while (0)
         if (per == 1) AXON_NORM_TYPE(1); else if (per == 2) AXON_NORM_TYPE(2); else if (per == 4) AXON_NORM_TYPE(4); else AXON_NORM_TYPE(8);
 #undef AXON_NORM_TYPE
@@ -407,11 +426,60 @@ AXON_API int axon_rmsnorm(const float* x, const float* gain, const int32_t* rows
     int threads = 128;
     while (threads < 1024 && threads * 4 < dim) threads *= 2;
     if (out_dtype == AXON_F32)
-        launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (float*)out, dim, eps, unit_offset);
+        launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (float*)out, dim, eps, unit_offset, fold);
     else if (out_dtype == AXON_BF16)
-        launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (__nv_bfloat16*)out, dim, eps, unit_offset);
+        launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (__nv_bfloat16*)out, dim, eps, unit_offset, fold);
     else { set_error("axon_rmsnorm: unknown output dtype %d", out_dtype); return AXON_BAD_ARGUMENT; }
     return launch_status("axon_rmsnorm");
+}
+
+AXON_API int axon_rmsnorm(const float* x, const float* gain, const int32_t* rows, void* out,
+                          int out_dtype, int n_rows, int dim, float eps, int unit_offset,
+                          cudaStream_t stream) {
+    return rmsnorm_launch(const_cast<float*>(x), gain, rows, out, out_dtype, n_rows, dim, eps, unit_offset,
+                          SplitFold{nullptr, nullptr, 0, 0}, stream);
+}
+
+// The norm of rows that a split-K product (axon_gemm_tc_small with `defer`) still owes its
+// partial sums: x[row] += the slabs in order (+ bias), written back, then normed.  With `rows`
+// only the gathered rows of x are brought up to date.
+AXON_API int axon_rmsnorm_fold(float* x, const float* gain, const int32_t* rows, void* out, int out_dtype,
+                               int n_rows, int dim, float eps, int unit_offset, const float* partial, int splits,
+                               int ntok, const float* bias, cudaStream_t stream) {
+    if (partial == nullptr || splits < 1 || ntok < 1) { set_error("axon_rmsnorm_fold: no partial sums given"); return AXON_BAD_ARGUMENT; }
+    if (rows == nullptr && n_rows > ntok) { set_error("axon_rmsnorm_fold: %d rows, partial sums for %d", n_rows, ntok); return AXON_BAD_ARGUMENT; }
+    return rmsnorm_launch(x, gain, rows, out, out_dtype, n_rows, dim, eps, unit_offset,
+                          SplitFold{partial, bias, splits, ntok}, stream);
+}
+
+// out[m][n] (= or +=) the partial sums of a deferred split-K product, for readers that cannot
+// fold them themselves.  out: float (store or accumulate) or bfloat16 (store).
+template <typename TO>
+__global__ void fold_partials_kernel(SplitFold fold, TO* __restrict__ out, int M, int N, int ldo, int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)M * N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N), n = (int)(i % N);
+        float v = fold.at(m, n);
+        TO* o = out + (long long)m * ldo + n;
+        if (accumulate) v += ldf(o);
+        stf(o, v);
+    }
+}
+
+AXON_API int axon_fold_partials(const float* partial, int splits, int ntok, const float* bias, void* out,
+                                int out_dtype, int M, int N, int ldo, int accumulate, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return AXON_OK;
+    if (partial == nullptr || splits < 1 || ntok < M) { set_error("axon_fold_partials: bad partial sums (splits %d, tokens %d of %d)", splits, M, ntok); return AXON_BAD_ARGUMENT; }
+    if (accumulate && out_dtype != AXON_F32) { set_error("axon_fold_partials: the residual is float"); return AXON_BAD_ARGUMENT; }
+    const SplitFold fold{partial, bias, splits, ntok};
+    const long long total = (long long)M * N;
+    const unsigned blocks = (unsigned)((total + 255) / 256 > 1184 ? 1184 : (total + 255) / 256);
+    if (out_dtype == AXON_F32) launch_pdl(fold_partials_kernel<float>, dim3(blocks), dim3(256), 0, stream, fold, (float*)out, M, N, ldo, accumulate);
+    else if (out_dtype == AXON_BF16) launch_pdl(fold_partials_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, fold, (__nv_bfloat16*)out, M, N, ldo, accumulate);
+    else { set_error("axon_fold_partials: unknown dtype %d", out_dtype); return AXON_BAD_ARGUMENT; }
+    return launch_status("axon_fold_partials");
 }
 
 template <typename TA, typename TW>
@@ -462,17 +530,22 @@ AXON_API int axon_rope_table(const int32_t* positions, const double* inv_freq, f
 AXON_API int axon_rope_kv_write(const float* qkv, const float* table, const int32_t* positions,
                                 const int32_t* token_slot, void* q_out, void* pool, int dtype,
                                 const AxonKvLayout* layout, int n, int heads, int rot, int adjacent,
-                                int write_kv, cudaStream_t stream) {
+                                int write_kv, const float* partial, int splits, int ntok, const float* bias,
+                                cudaStream_t stream) {
+    // partial != null: qkv is still owed the partial sums of a deferred split-K product
+    // (see axon_gemm_tc_small); they are folded here and `qkv` itself is not read
     if (n <= 0) return AXON_OK;
+    if (partial != nullptr && (splits < 1 || ntok < n)) { set_error("axon_rope_kv_write: bad partial sums (splits %d, tokens %d of %d)", splits, n, ntok); return AXON_BAD_ARGUMENT; }
+    const SplitFold fold{partial, partial ? bias : nullptr, splits, ntok};
     const int hd = layout->head_dim;
     if (hd % 2 || rot % 2 || rot > hd || rot < 0) { set_error("axon_rope_kv_write: head size %d / rotated size %d must be even and rot <= head", hd, rot); return AXON_BAD_ARGUMENT; }
     const int items = (heads + 2 * layout->kv_heads) * (hd / 2);
     dim3 grid(n, (items + 255) / 256 > 8 ? 8 : (items + 255) / 256);
     PagedKv kv = to_paged(layout);
     if (dtype == AXON_F32)
-        launch_pdl(rope_kv_write_kernel<float>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv);
+        launch_pdl(rope_kv_write_kernel<float>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv, fold);
     else if (dtype == AXON_BF16)
-        launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, kv, heads, rot, adjacent, write_kv);
+        launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, kv, heads, rot, adjacent, write_kv, fold);
     else { set_error("axon_rope_kv_write: unknown dtype %d", dtype); return AXON_BAD_ARGUMENT; }
     return launch_status("axon_rope_kv_write");
 }

@@ -6,7 +6,7 @@ from typing import Any, Dict, List, Optional, Union
 
 import torch
 
-from ..parts.base import Part, Runtime, StepContext, part_class
+from ..parts.base import Part, Runtime, StepContext, fold_owed, norm_owed, part_class
 from ..parts.spec import KvNeed, ModelSpec, PartSpec, StateNeed
 from ..weights.loader import expected_tensors
 
@@ -67,13 +67,21 @@ class DecoderModel:
         rt, n = self.rt, ctx.n_tokens
         x = rt.buffer("residual", (n, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx.tokens, x)
+        owed = None          # partial sums the residual is still owed by the last product into it
         for k, e in enumerate(self.spec.schedule):
-            self.blocks[e.layer].forward(x, ctx, cache.view(self.cache_owner(k)), e.cache_of is None)
+            block = self.blocks[e.layer]
+            if block.passes_owed:
+                owed = block.forward(x, ctx, cache.view(self.cache_owner(k)), e.cache_of is None, pending=owed)
+            else:
+                fold_owed(owed)
+                owed = None
+                block.forward(x, ctx, cache.view(self.cache_owner(k)), e.cache_of is None)
         if n_want == 0:
+            fold_owed(owed)
             return None
         # the head runs on the wanted rows only (src/lm.rs:114-126)
         h = rt.buffer("head_in", (n_want, self.spec.hidden_size))
-        self.final_norm.forward(x, h, rows=want_rows)
+        norm_owed(self.final_norm, x, h, owed, rows=want_rows)
         if logits_out is not None:
             logits = logits_out[:n_want]
         else:

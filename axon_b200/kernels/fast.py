@@ -7,6 +7,7 @@ checked here, before the launch, so a refusal never costs a failed launch.
 
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
@@ -48,14 +49,50 @@ def _split_scratch(device: torch.device):
     return got
 
 
-def _gemm_small(a, w, bias, out, epi, M, N, K) -> bool:
-    """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one."""
+class PendingFold:
+    """The partial sums a split-K product left in scratch instead of its output: whoever reads
+    ``out`` next adds them (``ops.rmsnorm(..., pending=)``, ``ops.rope_kv_write(..., pending=)``)
+    or calls ``ops.fold_partials``.  One may be outstanding per device (the scratch is shared);
+    starting another split product before it is claimed is an error, not a wrong result."""
+
+    def __init__(self, partial, splits, ntok, bias, out, accumulate):
+        self.partial, self.splits, self.ntok, self.bias = partial, splits, ntok, bias
+        self.out, self.accumulate = out, accumulate
+        self.claimed = False
+
+    def claim(self, tensor: torch.Tensor, accumulate: bool) -> None:
+        if self.claimed:
+            raise RuntimeError("these partial sums were folded already")
+        if tensor.data_ptr() != self.out.data_ptr() or accumulate != self.accumulate:
+            raise RuntimeError("partial sums folded into a tensor (or in a way) they were not made for")
+        self.claimed = True
+        if _OUTSTANDING.get(self.out.device) is self:
+            _OUTSTANDING[self.out.device] = None
+
+
+_OUTSTANDING = {}
+#: whether products for few rows may leave their partial sums to the reader of the output
+DEFER_FOLD = os.environ.get("AXON_DEFER_FOLD", "1") != "0"
+
+
+def _gemm_small(a, w, bias, out, epi, M, N, K, defer: bool = False):
+    """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one.  With ``defer`` a
+    split product returns a PendingFold instead of folding its partial sums itself."""
     if ENABLED["gemm_tc_small"] and not (M <= 8 and N <= MMA_SYNC_MAX_ROWS):
         partial, counters, _ = _split_scratch(a.device)
+        owed = _OUTSTANDING.get(a.device)
+        if owed is not None and not owed.claimed:
+            raise RuntimeError("a product's partial sums were never folded into its output "
+                               "(PendingFold dropped): the scratch they lie in is about to be overwritten")
+        plan = (ctypes.c_int * 3)()
         check(lib.cuda().axon_gemm_tc_small(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                             out.data_ptr(), epi, M, N, K, out.stride(0), partial.data_ptr(),
                                             partial.numel(), counters.data_ptr(), counters.numel(),
-                                            SPLIT_TARGET_CTAS, _stream()))
+                                            SPLIT_TARGET_CTAS, int(defer and DEFER_FOLD), plan, _stream()))
+        if plan[2]:
+            owed = PendingFold(partial, plan[0], plan[1], bias, out, epi == EPI_RESIDUAL)
+            _OUTSTANDING[a.device] = owed
+            return owed
         return True
     if ENABLED["gemm_small_m"]:
         check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
@@ -70,7 +107,9 @@ def _bf16_operands(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor],
-         accumulate: bool) -> bool:
+         accumulate: bool, defer: bool = False):
+    """True when it ran, False when it refuses; with ``defer`` possibly a PendingFold (the
+    output is still owed the partial sums of a split product)."""
     if not _bf16_operands(a, w):
         return False
     M, K = a.shape
@@ -85,8 +124,10 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         epi = EPI_STORE_BF16
     else:
         return False
-    if M <= SMALL_M and _gemm_small(a, w, bias, out, epi, M, N, K):
-        return True
+    if M <= SMALL_M:
+        ran = _gemm_small(a, w, bias, out, epi, M, N, K, defer and out.is_contiguous())
+        if ran:
+            return ran
     if ENABLED["gemm_tc"]:
         check(lib.cuda().axon_gemm_tc(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                       out.data_ptr(), epi, M, N, K, out.stride(0), _stream()))

@@ -41,10 +41,13 @@ P = c_void_p
 _SIGNATURES = {
     "axon_embed": [P, P, c_int, P, c_int, c_int, c_float, P],
     "axon_rmsnorm": [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P],
+    "axon_rmsnorm_fold": [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P, c_int, c_int, P, P],
+    "axon_fold_partials": [P, c_int, c_int, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_plain": [P, c_int, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "axon_swiglu": [P, P, c_int, c_int, c_int, P],
     "axon_rope_table": [P, P, P, c_int, c_int, c_float, P],
-    "axon_rope_kv_write": [P, P, P, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int, c_int, c_int, c_int, c_int, P],
+    "axon_rope_kv_write": [P, P, P, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int, c_int, c_int, c_int, c_int,
+                           P, c_int, c_int, P, P],
     "axon_attention_plain": [P, P, c_int, P, P, P, ctypes.POINTER(KvLayout), c_int, c_int, c_float, c_int, P],
     "axon_residual_add": [P, P, c_int, c_longlong, P],
     "axon_convert": [P, c_int, P, c_int, c_longlong, P],
@@ -55,7 +58,8 @@ _SIGNATURES = {
     "axon_gemm_small_m": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_tc": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_tc_status": [],
-    "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, P],
+    "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, c_int,
+                           ctypes.POINTER(c_int), P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
     "axon_attention_tc": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int, P],

@@ -16,13 +16,20 @@ from . import ops
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           accumulate: bool = False, precise: bool = False) -> None:
-    """``out = a @ w.T (+ bias)``; ``accumulate`` adds into a float32 ``out``."""
+           accumulate: bool = False, precise: bool = False, defer: bool = False):
+    """``out = a @ w.T (+ bias)``; ``accumulate`` adds into a float32 ``out``.
+
+    With ``defer`` the caller promises to hand what this returns to the next reader of
+    ``out``: None when ``out`` is complete, else a ``fast.PendingFold`` (the product was split
+    over K and its partial sums wait in scratch; ``ops.rmsnorm`` and ``ops.rope_kv_write``
+    fold them on their way, ``ops.fold_partials`` does it for any other reader)."""
     if not precise:
         from . import fast
-        if fast.gemm(a, w, out, bias, accumulate):
-            return
+        ran = fast.gemm(a, w, out, bias, accumulate, defer)
+        if ran:
+            return ran if isinstance(ran, fast.PendingFold) else None
     ops.gemm_plain(a, w, out, bias, accumulate)
+    return None
 
 
 def linear_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, rt) -> None:

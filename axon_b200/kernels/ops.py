@@ -77,14 +77,34 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: flo
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float,
-            rows: Optional[torch.Tensor] = None, unit_offset: bool = False) -> None:
-    """out[r] = norm(x[rows[r]] if rows is given else x[r]); x and gain are float32."""
+            rows: Optional[torch.Tensor] = None, unit_offset: bool = False, pending=None) -> None:
+    """out[r] = norm(x[rows[r]] if rows is given else x[r]); x and gain are float32.
+
+    ``pending`` (a ``fast.PendingFold`` whose output is ``x``): the partial sums that a
+    split-K product still owes ``x`` are added to the rows read (and written back) first."""
     _dev(x, gain, out, rows)
     if x.dtype != torch.float32 or gain.dtype != torch.float32:
         raise TypeError("rmsnorm reads a float32 residual and a float32 gain")
     n, dim = out.shape
+    if pending is not None:
+        pending.claim(x, accumulate=True)
+        check(lib.cuda().axon_rmsnorm_fold(_ptr(x), _ptr(gain), _ptr(rows), _ptr(out), dtype_code(out), n, dim,
+                                           float(eps), int(unit_offset), _ptr(pending.partial), pending.splits,
+                                           pending.ntok, _ptr(pending.bias), _stream()))
+        return
     check(lib.cuda().axon_rmsnorm(_ptr(x), _ptr(gain), _ptr(rows), _ptr(out), dtype_code(out), n, dim,
                                   float(eps), int(unit_offset), _stream()))
+
+
+def fold_partials(pending) -> None:
+    """Bring the output of a deferred split-K product up to date (for readers that cannot
+    fold the partial sums themselves)."""
+    out = pending.out
+    accumulate = pending.accumulate
+    pending.claim(out, accumulate=accumulate)
+    check(lib.cuda().axon_fold_partials(_ptr(pending.partial), pending.splits, pending.ntok, _ptr(pending.bias),
+                                        _ptr(out), dtype_code(out), out.shape[0], out.shape[1], out.stride(0),
+                                        int(accumulate), _stream()))
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -121,16 +141,23 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Ten
 
 def rope_kv_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions: torch.Tensor,
                   token_slot: torch.Tensor, q_out: torch.Tensor, kv: KvView, heads: int, rot: int,
-                  adjacent: bool = False, write_kv: bool = True) -> None:
+                  adjacent: bool = False, write_kv: bool = True, pending=None) -> None:
+    """``pending`` (a ``fast.PendingFold`` whose output is ``qkv``): the product is still in
+    partial sums; they are folded here (with the bias) and ``qkv`` itself is not read."""
     _dev(qkv, table, positions, token_slot, q_out, kv.pool)
     n = q_out.shape[0]
     if qkv.dtype != torch.float32 or qkv.shape[1] != (heads + 2 * kv.kv_heads) * kv.head_dim:
         raise ValueError("rope_kv_write reads float32 [n][(heads + 2 kv_heads) * head_dim]")
     if q_out.dtype != kv.pool.dtype:
         raise TypeError("queries and the cache have one dtype")
+    if pending is not None:
+        pending.claim(qkv, accumulate=False)
     check(lib.cuda().axon_rope_kv_write(_ptr(qkv), _ptr(table), _ptr(positions), _ptr(token_slot), _ptr(q_out),
                                         _ptr(kv.pool), dtype_code(q_out), kv._ref, n, heads, rot, int(adjacent),
-                                        int(write_kv), _stream()))
+                                        int(write_kv), None if pending is None else _ptr(pending.partial),
+                                        0 if pending is None else pending.splits,
+                                        0 if pending is None else pending.ntok,
+                                        None if pending is None else _ptr(pending.bias), _stream()))
 
 
 def attention_plain(q: torch.Tensor, kv: KvView, positions: torch.Tensor, token_slot: torch.Tensor,

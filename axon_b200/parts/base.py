@@ -113,6 +113,17 @@ class Part:
     #: branching on device data, no allocation.  Steps of a model whose parts are all safe
     #: may be captured into CUDA graphs.
     graph_safe: ClassVar[bool] = False
+    #: Owed sums.  A product for few rows may be split over K and leave its partial sums in
+    #: scratch for the next reader of its output (``kernels.fast.PendingFold``), which saves
+    #: that product a pass.  A mixer or feed-forward whose class sets ``may_defer`` takes
+    #: ``defer=True`` in ``forward`` and then returns what its last product into the residual
+    #: still owes (or None); a norm whose class sets ``folds_owed`` takes ``pending=`` and adds
+    #: it to the rows it reads; a block whose class sets ``passes_owed`` takes ``pending=`` for
+    #: its input and returns what its output is owed.  Parts that set none of these never see
+    #: a PendingFold: their caller folds first (``fold_owed``).
+    may_defer: ClassVar[bool] = False
+    folds_owed: ClassVar[bool] = False
+    passes_owed: ClassVar[bool] = False
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -151,6 +162,22 @@ class FeedForward(Part):
         from ..kernels import ops
         out = self.compute(h, ctx)
         ops.residual_add(x, out.contiguous())
+
+
+def fold_owed(pending) -> None:
+    """Bring a tensor up to date with the partial sums it is still owed (None: nothing to do)."""
+    if pending is not None:
+        from ..kernels import ops
+        ops.fold_partials(pending)
+
+
+def norm_owed(norm: Part, x: torch.Tensor, out: torch.Tensor, pending, **kw) -> None:
+    """``norm.forward(x, out)`` where ``x`` may still be owed partial sums."""
+    if pending is not None and norm.folds_owed:
+        norm.forward(x, out, pending=pending, **kw)
+    else:
+        fold_owed(pending)
+        norm.forward(x, out, **kw)
 
 
 _REGISTRY: Dict[Tuple[str, str], Type[Part]] = {}

@@ -15,7 +15,7 @@ import torch
 
 from ..kernels import linear as _linear
 from ..kernels import ops
-from .base import FeedForward, Mixer, Part, Runtime, StepContext, register_part
+from .base import FeedForward, Mixer, Part, Runtime, StepContext, fold_owed, norm_owed, register_part
 from .spec import KvNeed, PartSpec, TensorDecl
 
 
@@ -29,6 +29,7 @@ class RMSNorm(Part):
 
     category, kind = "norm", "rmsnorm"
     graph_safe = True
+    folds_owed = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -41,8 +42,8 @@ class RMSNorm(Part):
         self.unit_offset = bool(spec.params.get("unit_offset", False))
         self.gain = tensors["gain"]
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-        ops.rmsnorm(x, self.gain, out, self.eps, rows=rows, unit_offset=self.unit_offset)
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None, pending=None) -> None:
+        ops.rmsnorm(x, self.gain, out, self.eps, rows=rows, unit_offset=self.unit_offset, pending=pending)
 
 
 @register_part
@@ -106,6 +107,7 @@ class Attention(Mixer):
 
     category, kind = "mixer", "attention"
     graph_safe = True
+    may_defer = True
     nested = {"position": "position"}
 
     @classmethod
@@ -144,19 +146,20 @@ class Attention(Mixer):
         self.b_o = tensors.get("o_bias") if p.get("out_bias") else None
         self.position = build(spec.parts["position"]) if "position" in spec.parts else None
 
-    def forward(self, h, x, ctx: StepContext, cache: ops.KvView, write_cache: bool = True) -> None:
+    def forward(self, h, x, ctx: StepContext, cache: ops.KvView, write_cache: bool = True, defer: bool = False):
         rt, n = self.rt, ctx.n_tokens
         qkv = rt.buffer("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
-        _linear.linear(h, self.w_qkv, qkv, bias=self.b_qkv, precise=rt.precise)
+        # a product split over K leaves its partial sums to the kernel that reads its output
+        owed = _linear.linear(h, self.w_qkv, qkv, bias=self.b_qkv, precise=rt.precise, defer=True)
         table, rot, adjacent = None, 0, False
         if self.position is not None:
             table, rot, adjacent = self.position.rotation(ctx), self.position.rot, self.position.adjacent
         q = rt.buffer("q", (n, self.q_dim))
         ops.rope_kv_write(qkv, table, ctx.positions, ctx.token_slot, q, cache, self.heads, rot, adjacent,
-                          write_kv=write_cache)
+                          write_kv=write_cache, pending=owed)
         att = rt.buffer("att", (n, self.q_dim))
         _linear.attention(q, cache, ctx, att, self.heads, self.scale, precise=rt.precise)
-        _linear.linear(att, self.w_o, x, bias=self.b_o, accumulate=True, precise=rt.precise)
+        return _linear.linear(att, self.w_o, x, bias=self.b_o, accumulate=True, precise=rt.precise, defer=defer)
 
 
 @register_part
@@ -171,6 +174,7 @@ class SwiGLU(FeedForward):
 
     category, kind = "ffn", "swiglu"
     graph_safe = True
+    may_defer = True
 
     @classmethod
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
@@ -183,11 +187,11 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.stack([tensors["gate"], tensors["up"]], dim=1).reshape(2 * self.ffn, self.hidden).contiguous()
         self.w_down = tensors["down"]
 
-    def forward(self, h, x, ctx: StepContext) -> None:
+    def forward(self, h, x, ctx: StepContext, defer: bool = False):
         rt, n = self.rt, h.shape[0]
         act = rt.buffer("ffn_act", (n, self.ffn))
         _linear.linear_swiglu(h, self.w_gate_up, act, rt)
-        _linear.linear(act, self.w_down, x, accumulate=True, precise=rt.precise)
+        return _linear.linear(act, self.w_down, x, accumulate=True, precise=rt.precise, defer=defer)
 
 
 @register_part
@@ -197,6 +201,7 @@ class PreNormBlock(Part):
 
     category, kind = "block", "prenorm"
     graph_safe = True
+    passes_owed = True
     nested = {"norm_mixer": "norm", "mixer": "mixer", "norm_ffn": "norm", "ffn": "ffn"}
 
     def __init__(self, spec, tensors, rt, build):
@@ -206,12 +211,19 @@ class PreNormBlock(Part):
         self.norm_ffn = build(spec.parts["norm_ffn"])
         self.ffn = build(spec.parts["ffn"])
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, write_cache: bool = True) -> None:
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, write_cache: bool = True, pending=None):
+        """``pending``: what ``x`` is still owed on entry; returns what it is owed on exit."""
         h = self.rt.buffer("block_h", tuple(x.shape))
-        self.norm_mixer.forward(x, h)
-        self.mixer.forward(h, x, ctx, cache, write_cache)
-        self.norm_ffn.forward(x, h)
+        norm_owed(self.norm_mixer, x, h, pending)
+        if self.mixer.may_defer:
+            owed = self.mixer.forward(h, x, ctx, cache, write_cache, defer=True)
+        else:
+            owed = self.mixer.forward(h, x, ctx, cache, write_cache)
+        norm_owed(self.norm_ffn, x, h, owed)
+        if self.ffn.may_defer:
+            return self.ffn.forward(h, x, ctx, defer=True)
         self.ffn.forward(h, x, ctx)
+        return None
 
 
 @register_part

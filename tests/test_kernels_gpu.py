@@ -451,6 +451,87 @@ def test_gemm_tensor_core_output_paths(ops, M, N, K):
     assert fast.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 3584, 1024), (1, 1002, 2048), (33, 640, 4096), (64, 256, 8192)])
+def test_split_product_leaves_its_fold_to_the_reader(ops, M, N, K):
+    """A product for few rows that is split over K may leave its partial sums to whoever reads the
+    output next.  Every reader (the norm, the generic fold) gives the numbers of the product that
+    folds by itself, bit for bit; a PendingFold that nobody claims is an error at the next product."""
+    from axon_b200.kernels import fast
+    a = rand(M, K, dtype=torch.bfloat16, seed=110)
+    w = rand(N, K, dtype=torch.bfloat16, seed=111, std=0.1)
+    bias = rand(N, seed=112)
+    res = rand(M, N, seed=113)
+    want = res.clone()
+    assert fast.gemm(a, w, want, bias, True) is True                 # folds by itself
+    # the generic fold
+    got = res.clone()
+    owed = fast.gemm(a, w, got, bias, True, defer=True)
+    assert isinstance(owed, fast.PendingFold) and owed.splits > 1, "this shape is meant to split"
+    assert torch.equal(got, res), "a deferred product must not touch its output"
+    ops.fold_partials(owed)
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        ops.fold_partials(owed)                                       # claimed once
+    # stored, not accumulated, into bfloat16-free float output
+    plain = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    assert fast.gemm(a, w, plain, bias, False) is True
+    got = torch.full((M, N), 3.0, dtype=torch.float32, device=DEV)
+    owed = fast.gemm(a, w, got, bias, False, defer=True)
+    ops.fold_partials(owed)
+    assert torch.equal(got, plain)
+    # the norm as reader: x brought up to date and normed in one kernel, all rows or gathered ones
+    gain = rand(N, seed=114) * 0.1 + 1.0
+    h_want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(want, gain, h_want, 1e-6)
+    x = res.clone()
+    owed = fast.gemm(a, w, x, bias, True, defer=True)
+    h = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, gain, h, 1e-6, pending=owed)
+    assert torch.equal(x, want) and torch.equal(h, h_want)
+    rows = torch.tensor([M - 1, 0], dtype=torch.int32, device=DEV)
+    x = res.clone()
+    owed = fast.gemm(a, w, x, bias, True, defer=True)
+    h2 = torch.empty(2, N, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x, gain, h2, 1e-6, rows=rows, pending=owed)
+    assert torch.equal(h2, h_want[rows.long()]) and torch.equal(x[rows.long()], want[rows.long()])
+    # dropped: the next split product refuses to overwrite the scratch
+    owed = fast.gemm(a, w, res.clone(), bias, True, defer=True)
+    with pytest.raises(RuntimeError):
+        fast.gemm(a, w, res.clone(), bias, True)
+    owed.claimed = True
+    with pytest.raises(RuntimeError):                                 # folded into the wrong tensor
+        o2 = fast.gemm(a, w, res.clone(), bias, True, defer=True)
+        ops.rmsnorm(res.clone(), gain, h, 1e-6, pending=o2)
+    o2.claimed = True
+    assert fast.gemm_tc_status() == 0
+
+
+def test_rotation_reads_a_split_product(ops):
+    """rope_kv_write folding the partial sums of the q/k/v product gives what it gives on the folded product."""
+    from axon_b200.kernels import fast
+    heads, kv_heads, hd, n, ps = 6, 2, 64, 5, 4
+    width = (heads + 2 * kv_heads) * hd
+    a = rand(n, 2048, dtype=torch.bfloat16, seed=120)
+    w = rand(width, 2048, dtype=torch.bfloat16, seed=121, std=0.1)
+    bias = rand(width, seed=122)
+    positions = torch.tensor([0, 1, 2, 7, 8], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    table = torch.empty(n, hd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions, inv.to(DEV), table)
+    outs = []
+    for defer in (False, True):
+        view, _ = make_cache(ops, torch.bfloat16, kv_heads, hd, ps, 8, 2, 16, seed=9)
+        qkv = torch.full((n, width), 2.0, dtype=torch.float32, device=DEV)
+        owed = fast.gemm(a, w, qkv, bias, False, defer=defer)
+        assert isinstance(owed, fast.PendingFold) == defer
+        q = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+        ops.rope_kv_write(qkv, table, positions, slots, q, view, heads, hd, pending=owed if defer else None)
+        outs.append((q, view.pool.clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][1].abs().sum() > 0
+
+
 def _ctx_for(segs):
     """A StepContext for segments [(slot, q_len, kv_len)] with tokens flattened in order."""
     from axon_b200.parts import Runtime, StepContext
