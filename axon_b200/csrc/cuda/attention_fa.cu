@@ -39,6 +39,7 @@ struct FaParams {
     PagedKv kv;
     int n_segments, heads, group, tokens_per_tile, n_splits, window;
     float scale_log2;            // scale * log2(e)
+    int cluster;                 // the splits of an (item, kv head) are one thread-block cluster and fold in shared memory
 };
 
 template <int HD> struct Swz {
@@ -144,6 +145,14 @@ attention_fa_kernel(const FaParams p) {
             if (tile < t_end && (tile + 1) * FA_BN <= new_from)
                 load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
             cp_async_commit();
+        }
+        // the older tiles beyond those: into L2 (two threads per key: its K row and its V row)
+        for (int tile = t_begin + NST - 1; tile < t_end && (tile + 1) * FA_BN <= new_from; ++tile) {
+            const int r = threadIdx.x >> 1;
+            if (r < FA_BN) {
+                const __nv_bfloat16* row = p.pool + p.kv.row(slot, tile * FA_BN + r, kvh) + ((threadIdx.x & 1) ? p.kv.v_offset : 0);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(HD * 2) : "memory");
+            }
         }
         pdl_wait();
     }
@@ -332,6 +341,74 @@ attention_fa_kernel(const FaParams p) {
         mml[(warp * 16 + g + 8) * 2] = m_b; mml[(warp * 16 + g + 8) * 2 + 1] = l_b;
     }
     __syncthreads();
+    if (p.cluster) {
+        // The splits of this (item, kv head) are the CTAs of one cluster: each sends its merged
+        // partial to the first CTA's shared memory, which folds them in split order.  No
+        // scratch in global memory, no second kernel.
+        constexpr int EPT = 16 * HD / FA_THREADS;
+        float accv[EPT], mv[EPT], lv[EPT];
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
+            const float use = (m == -INFINITY) ? 0.f : m;
+            float l = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(mml[(w * 16 + r) * 2] - use);
+                l += mml[(w * 16 + r) * 2 + 1] * f;
+                acc += mo[(w * 16 + r) * HD + d] * f;
+            }
+            accv[k] = acc; mv[k] = m; lv[k] = l;
+        }
+        // every CTA of the cluster is done with its tiles and merge buffers: the first one's
+        // shared memory is free to receive
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        uint32_t lead;      // the first CTA's shared memory: [splits][16][HD] sums, then [splits][16][2] maxima and weights
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(lead) : "r"(smem), "r"(0));
+        const uint32_t lead_ml = lead + (uint32_t)p.n_splits * 16 * HD * 4;
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
+            if (r >= rows_used) continue;
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead + (uint32_t)((split * 16 + r) * HD + d) * 4), "f"(accv[k]) : "memory");
+            if (d == 0) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead_ml + (uint32_t)((split * 16 + r) * 2) * 4), "f"(mv[k]) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead_ml + (uint32_t)((split * 16 + r) * 2 + 1) * 4), "f"(lv[k]) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (split != 0) return;
+        float* red_o = reinterpret_cast<float*>(smem_raw);
+        float* red_ml = red_o + p.n_splits * 16 * HD;
+        if (threadIdx.x < rows_used) {
+            const int r = threadIdx.x;
+            float m = -INFINITY;
+            for (int s2 = 0; s2 < p.n_splits; ++s2) m = fmaxf(m, red_ml[(s2 * 16 + r) * 2]);
+            const float use = (m == -INFINITY) ? 0.f : m;
+            float l = 0.f;
+            for (int s2 = 0; s2 < p.n_splits; ++s2) {
+                const float f = exp2f(red_ml[(s2 * 16 + r) * 2] - use);
+                l += red_ml[(s2 * 16 + r) * 2 + 1] * f;
+                red_ml[(s2 * 16 + r) * 2] = f;
+            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            for (int s2 = 0; s2 < p.n_splits; ++s2) red_ml[(s2 * 16 + r) * 2] *= inv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
+            if (r >= rows_used) continue;
+            float acc = 0.f;
+            for (int s2 = 0; s2 < p.n_splits; ++s2) acc += red_o[(s2 * 16 + r) * HD + d] * red_ml[(s2 * 16 + r) * 2];
+            const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
+            p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(acc);
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < 16 * HD; e += FA_THREADS) {
         const int r = e / HD, d = e % HD;
         if (r >= rows_used) continue;
@@ -514,6 +591,26 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
         configured = true;
     }
     dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);
+    if (DECODE && p.cluster) {
+        // the splits of one (item, kv head) form a cluster (grid z)
+        static_assert(!DECODE || (size_t)8 * 16 * (HD + 2) * 4 <= smem, "the first CTA's shared memory takes every split's partial");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(FA_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = (unsigned)p.n_splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        cudaLaunchKernelEx(&cfg, attention_fa_kernel<HD, DECODE>, p);
+        return launch_status("axon_attention_fa");
+    }
     launch_pdl(attention_fa_kernel<HD, DECODE>, grid, dim3(FA_THREADS), smem, stream, p);
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
@@ -555,14 +652,17 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
     const int group = heads / kvh, bm = decode ? 16 : 64;
     if (tokens_per_tile < 1 || tokens_per_tile * group > bm) { set_error("axon_attention_fa: %d tokens x %d heads do not fit a tile of %d rows", tokens_per_tile, group, bm); return AXON_BAD_ARGUMENT; }
     if (n_splits < 1 || n_splits > FA_MAX_SPLITS || (!decode && n_splits != 1)) { set_error("axon_attention_fa: bad split count %d (1..%d; 1 for prefill tiles)", n_splits, FA_MAX_SPLITS); return AXON_BAD_ARGUMENT; }
-    if (n_splits > 1 && scratch == nullptr) { set_error("axon_attention_fa: splits need scratch memory"); return AXON_BAD_ARGUMENT; }
+    // splits without scratch: the (at most 8) splits of an (item, kv head) run as one thread-block
+    // cluster and fold through the first CTA's shared memory
+    if (n_splits > 8 && scratch == nullptr) { set_error("axon_attention_fa: more than 8 splits need scratch memory"); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) { set_error("axon_attention_fa: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     FaParams p;
     p.q = (const __nv_bfloat16*)q; p.pool = (const __nv_bfloat16*)pool; p.out = (__nv_bfloat16*)out;
     p.segments = segments; p.items = items;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (long long)n_items * kvh * n_splits * 16 * hd : nullptr;
-    p.counters = (n_splits > 1) ? counters : nullptr;
+    p.counters = (n_splits > 1 && scratch) ? counters : nullptr;
+    p.cluster = (decode && n_splits > 1 && scratch == nullptr) ? 1 : 0;
     p.kv.block_table = layout->block_table; p.kv.table_stride = layout->table_stride; p.kv.page_size = layout->page_size;
     p.kv.kv_heads = kvh; p.kv.head_dim = hd; p.kv.page_stride = layout->page_stride;
     p.kv.entry_offset = layout->entry_offset; p.kv.v_offset = layout->v_offset;

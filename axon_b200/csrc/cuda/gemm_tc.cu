@@ -393,6 +393,8 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
                 tma_load_2d(smem_base + i * STAGE_BYTES, &map_w, (ks_begin + i) * TC_BK, n0, full0 + 8 * i);
             }
+            // (asking for further boxes into L2 here was measured: it slows the step down, the more
+            // boxes the more, because the requests queue ahead of the loads that follow)
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
                 tma_load_2d(smem_base + i * STAGE_BYTES + W_BYTES, &map_x, (ks_begin + i) * TC_BK, 0, full0 + 8 * i);

@@ -282,6 +282,47 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
     }
 }
 
+// The same for the common layout (pairs (i, i + head/2), the whole head rotated, head % 8 == 0,
+// 16-byte aligned rows): a thread owns four consecutive pairs, reads them as float4 and stores
+// 8 bytes each, instead of single elements.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict__ table,
+                                         const int32_t* __restrict__ positions,
+                                         const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
+                                         T* __restrict__ pool, PagedKv kv, int heads, int write_kv, SplitFold fold) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int hd = kv.head_dim, half = hd / 2, quads = half / 4;
+    const int q_dim = heads * hd, kv_dim = kv.kv_heads * hd;
+    const float* row = qkv + (long long)t * (q_dim + 2 * kv_dim);
+    const int pos = positions[t], slot = token_slot[t];
+    const int items = (heads + 2 * kv.kv_heads) * quads;
+    for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
+        const int h = it / quads, i0 = (it % quads) * 4;
+        const bool is_q = h < heads, is_v = h >= heads + kv.kv_heads;
+        if (!is_q && !write_kv) continue;
+        const int col = h * hd;                           // q heads, then k heads, then v heads
+        float4 a, b;
+        if (fold.partial) { a = fold.at4(t, col + i0); b = fold.at4(t, col + half + i0); }
+        else { a = *reinterpret_cast<const float4*>(row + col + i0); b = *reinterpret_cast<const float4*>(row + col + half + i0); }
+        float4 ra = a, rb = b;
+        if (!is_v) {
+            const float4 c01 = *reinterpret_cast<const float4*>(table + (long long)t * half + i0);       // cos0 sin0 cos1 sin1
+            const float4 c23 = *reinterpret_cast<const float4*>(table + (long long)t * half + i0 + 2);
+            ra.x = a.x * c01.x - b.x * c01.y; rb.x = a.x * c01.y + b.x * c01.x;
+            ra.y = a.y * c01.z - b.y * c01.w; rb.y = a.y * c01.w + b.y * c01.z;
+            ra.z = a.z * c23.x - b.z * c23.y; rb.z = a.z * c23.y + b.z * c23.x;
+            ra.w = a.w * c23.z - b.w * c23.w; rb.w = a.w * c23.w + b.w * c23.z;
+        }
+        T* dst;
+        if (is_q) dst = q_out + (long long)t * q_dim + col;
+        else dst = pool + kv.row(slot, pos, is_v ? h - heads - kv.kv_heads : h - heads) + (is_v ? kv.v_offset : 0);
+        store4(dst + i0, ra.x, ra.y, ra.z, ra.w);
+        store4(dst + half + i0, rb.x, rb.y, rb.z, rb.w);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Causal attention over the paged cache, one warp per (token, query head).
 // Keys kv_begin..pos are folded 32 at a time in ascending order with a running
@@ -414,6 +455,9 @@ static int rmsnorm_launch(float* x, const float* gain, const int32_t* rows, void
         (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)fold.partial | (uintptr_t)fold.bias) & 15) == 0) {
         // whole float4s, at most 8 per thread: the kernel that reads the row once
         int per = (n4 + 1023) / 1024;
+        // few rows: as many threads per row as there are float4s (the shortest chain); many rows:
+        // four float4s per thread, so that several rows fit an SM and enough bytes are in flight
+        if (n_rows > 4 * 148 && per < 4 && n4 >= 4 * 64) per = 4;
         per = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
         int threads = ((n4 + per - 1) / per + 31) / 32 * 32;
 #define AXON_NORM_CASE(TO, VPT) launch_pdl(rmsnorm_vec_kernel<TO, VPT>, dim3(n_rows), dim3(threads), 0, stream, x, gain, rows, (TO*)out, dim, eps, unit_offset, fold)
@@ -539,9 +583,22 @@ AXON_API int axon_rope_kv_write(const float* qkv, const float* table, const int3
     const SplitFold fold{partial, partial ? bias : nullptr, splits, ntok};
     const int hd = layout->head_dim;
     if (hd % 2 || rot % 2 || rot > hd || rot < 0) { set_error("axon_rope_kv_write: head size %d / rotated size %d must be even and rot <= head", hd, rot); return AXON_BAD_ARGUMENT; }
+    PagedKv kv = to_paged(layout);
+    if (table != nullptr && !adjacent && rot == hd && hd % 8 == 0 &&
+        (((uintptr_t)qkv | (uintptr_t)table | (uintptr_t)q_out | (uintptr_t)pool | (uintptr_t)partial | (uintptr_t)bias) & 15) == 0 &&
+        (layout->page_stride * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0 && (layout->entry_offset * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0 &&
+        (layout->v_offset * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0) {
+        const int quads = (heads + 2 * layout->kv_heads) * (hd / 8);
+        dim3 vgrid(n, (quads + 255) / 256 > 8 ? 8 : (quads + 255) / 256);
+        if (dtype == AXON_F32)
+            launch_pdl(rope_kv_write_vec_kernel<float>, vgrid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, write_kv, fold);
+        else if (dtype == AXON_BF16)
+            launch_pdl(rope_kv_write_vec_kernel<__nv_bfloat16>, vgrid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, kv, heads, write_kv, fold);
+        else { set_error("axon_rope_kv_write: unknown dtype %d", dtype); return AXON_BAD_ARGUMENT; }
+        return launch_status("axon_rope_kv_write");
+    }
     const int items = (heads + 2 * layout->kv_heads) * (hd / 2);
     dim3 grid(n, (items + 255) / 256 > 8 ? 8 : (items + 255) / 256);
-    PagedKv kv = to_paged(layout);
     if (dtype == AXON_F32)
         launch_pdl(rope_kv_write_kernel<float>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv, fold);
     else if (dtype == AXON_BF16)

@@ -167,6 +167,10 @@ FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 2 * 148))
 #: sizes the second kernel is a little faster up to batch 8 and equal at 64, because it overlaps
 #: with the kernels around it while the in-kernel fold lengthens the slowest CTA)
 FA_FOLD_IN_KERNEL = os.environ.get("AXON_FA_FOLD_IN_KERNEL", "0") != "0"
+#: whether few splits fold through a thread-block cluster's shared memory instead of scratch and a
+#: second kernel.  Off: measured at 7B sizes and batch 8 the step is 6 % slower with it, because a
+#: cluster of 8 CTAs waits until 8 SMs of one GPC have room at once, beside the products' CTAs.
+FA_CLUSTER = os.environ.get("AXON_FA_CLUSTER", "0") != "0"
 SM_COUNT = 148
 
 
@@ -233,7 +237,11 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
         splits = max(1, min(tiles, FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads))))
         scratch = None
         counters = _split_scratch(q.device)[2]
-        if splits > 1:
+        # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
+        # no second kernel); longer contexts keep more, independent splits
+        if FA_CLUSTER and splits > 1 and -(-tiles // min(splits, 8)) <= 16:
+            splits = min(splits, 8)
+        elif splits > 1:
             # sized for the most splits this batch can get, so that the buffer never moves
             # while the contexts grow (captured graphs hold its address)
             most = min(FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads)))

@@ -552,14 +552,16 @@ def _ctx_for(segs):
 @pytest.mark.parametrize("heads,kv_heads,hd,ps,window", [
     (4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (6, 2, 64, 8, 0), (28, 4, 128, 16, 0), (8, 8, 128, 16, 0),
     (40, 2, 64, 16, 0), (7, 1, 128, 1, 0), (6, 2, 64, 16, 70), (4, 2, 128, 16, 9)])
-@pytest.mark.parametrize("fold_in_kernel,tcgen05", [(False, True), (True, True), (False, False)])
-def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold_in_kernel, tcgen05, monkeypatch):
+@pytest.mark.parametrize("fold,tcgen05", [("cluster", True), ("second_kernel", True), ("last_cta", True), ("cluster", False)])
+def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold, tcgen05, monkeypatch):
     """The tensor-core kernel on a mixed batch: decoded tokens at short and long contexts
     (one key; several splits), two-token portions, a whole prompt, a portion in the middle
     of a long request.  One key far back gets a large score so that a wrong page or a
     dropped tile shows."""
     from axon_b200.kernels import fast
-    monkeypatch.setattr(fast, "FA_FOLD_IN_KERNEL", fold_in_kernel)   # both ways of folding the key splits
+    # the three ways of folding the key splits of a decoded token
+    monkeypatch.setattr(fast, "FA_CLUSTER", fold == "cluster")
+    monkeypatch.setattr(fast, "FA_FOLD_IN_KERNEL", fold == "last_cta")
     # prompt portions at head size 128: the tcgen05 kernel, or the mma.sync one as for other head sizes
     monkeypatch.setitem(fast.ENABLED, "attention_tc", tcgen05)
     # (q_len, kv_len) per request
