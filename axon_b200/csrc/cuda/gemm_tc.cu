@@ -622,7 +622,9 @@ static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, cons
 // The tile shape for a product: among (rows 128 or 256) x (columns 128, 192, 224, 256) the one
 // with the least modelled time.  The model: operand bytes all CTAs pull from L2
 // ((rows + columns) * K * 2 per tile) against what L2 delivers, and whole waves of tiles on 148
-// SMs against the tensor rate; it reproduces the measured 128 x 256 times within 5 %.
+// SMs against the rate one SM sustains on a 256 x 256 tile (12.7 TFLOP/s measured at K = 18944).
+// It picks 256 x 224 where that fills 128 SMs instead of 112 (3584 columns: measured 186 us
+// against 197 us at K = 18944) and 256 x 256 for 4608 and 37888 columns.
 struct TileShape { int rm, bn; };
 static TileShape choose_tile(int M, int N, int K) {
     const int bns[4] = {256, 224, 192, 128};
@@ -634,7 +636,7 @@ static TileShape choose_tile(int M, int N, int K) {
             const long long tiles = (long long)((M + rows - 1) / rows) * ((N + bn - 1) / bn);
             const double feed = (double)tiles * (rows + bn) * K * 2 / 12.9e12;
             const double waves = (double)((tiles + 147) / 148);
-            const double compute = waves * (double)rows * bn * K * 2 / 15.2e12;
+            const double compute = waves * (double)rows * bn * K * 2 / 12.7e12;
             const double t = (feed > compute ? feed : compute) + 3e-6 * waves;
             if (t < best_t * 0.98) { best_t = t; best = TileShape{rm, bn}; }
         }

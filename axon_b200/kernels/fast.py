@@ -205,8 +205,7 @@ def _attention_items(ctx, group: int, pre_rows: int = 64):
     # long ones must not be the last to start
     for _, s, t0 in sorted(pre_work, reverse=True):
         pre += [s, t0]
-    dev = ctx.tokens.device
-    both = torch.tensor(dec + pre, dtype=torch.int32, device=dev) if dec or pre else None
+    both = ctx.rt.upload_i32(f"fa_items_{group}_{pre_rows}", dec + pre) if dec or pre else None
     got = {"dec": both[:len(dec)] if dec else None, "n_dec": len(dec) // 2, "dec_kv": dec_kv,
            "pre": both[len(dec):] if pre else None, "n_pre": len(pre) // 2,
            "tpt_dec": tpt_dec, "tpt_pre": tpt_pre}

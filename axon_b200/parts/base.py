@@ -46,6 +46,7 @@ class Runtime:
         #: the true 32-bit path: plain FFMA kernels everywhere
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._pinned: Dict[str, Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = {}
         #: raised whenever an existing scratch buffer is replaced by a larger one: addresses
         #: handed out before are stale from then on (captured CUDA graphs must be dropped)
         self.generation = 0
@@ -62,6 +63,25 @@ class Runtime:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
         return buf[:n].view(shape)
+
+    def upload_i32(self, name: str, values) -> torch.Tensor:
+        """Host integers to a named device buffer through pinned memory, without blocking the
+        host (a tensor made from a Python list goes through pageable memory and stalls the
+        stream).  The pinned copy of a name is reused once its last transfer has finished."""
+        import numpy as np
+        n = len(values)
+        host, event = self._pinned.get(name, (None, None))
+        if event is not None:
+            event.synchronize()
+        if host is None or host.numel() < n:
+            host = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+        host.numpy()[:n] = np.asarray(values, dtype=np.int32)
+        dev = self.buffer(name, (n,), torch.int32)
+        dev.copy_(host[:n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._pinned[name] = (host, event)
+        return dev
 
     def release_buffers(self) -> None:
         self._buffers.clear()
