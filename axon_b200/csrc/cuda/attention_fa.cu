@@ -40,7 +40,61 @@ struct FaParams {
     int n_segments, heads, group, tokens_per_tile, n_splits, window;
     float scale_log2;            // scale * log2(e)
     int cluster;                 // the splits of an (item, kv head) are one thread-block cluster and fold in shared memory
+    // Decode steps may hand over the q/k/v product itself instead of rotated queries and a written
+    // cache (qkv != nullptr): every CTA rotates its own queries, and the CTA whose keys include
+    // the new positions rotates and writes their keys and values before it reads them.
+    const float* qkv;            // [tokens][qkv_width] float (biases added), or owed the sums in `fold`
+    SplitFold fold;
+    const float2* table;         // [tokens][hd / 2] (cos, sin), or nullptr: no rotation
+    __nv_bfloat16* pool_rw;      // the cache, writable
+    int qkv_width, write_kv;
 };
+
+// Four consecutive values of the q/k/v product of token t from column col (col % 4 == 0).
+__device__ __forceinline__ float4 qkv_at4(const FaParams& p, int t, int col) {
+    if (p.fold.partial) return p.fold.at4(t, col);
+    return *reinterpret_cast<const float4*>(p.qkv + (long long)t * p.qkv_width + col);
+}
+// Pairs (i, i + hd/2), i = i0 .. i0 + 3, of one head starting at column `col`, rotated by the
+// token's angles (or passed through when there is no table or `rotate` is false).
+__device__ __forceinline__ void rotated_quads(const FaParams& p, int t, int col, int half, int i0, bool rotate,
+                                              float4& ra, float4& rb) {
+    float4 a, b;
+    if (p.fold.partial && p.fold.splits <= 8) {
+        // both halves' slabs in one batch of loads
+        const float4* pa = reinterpret_cast<const float4*>(p.fold.partial + ((long long)((col + i0) >> 7) * p.fold.splits * p.fold.ntok + t) * 128 + ((col + i0) & 127));
+        const float4* pb = reinterpret_cast<const float4*>(p.fold.partial + ((long long)((col + half + i0) >> 7) * p.fold.splits * p.fold.ntok + t) * 128 + ((col + half + i0) & 127));
+        const long long step = (long long)p.fold.ntok * 32;
+        float4 ta[8], tb[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            ta[q] = q < p.fold.splits ? __ldcg(pa + q * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+            tb[q] = q < p.fold.splits ? __ldcg(pb + q * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            a.x += ta[q].x; a.y += ta[q].y; a.z += ta[q].z; a.w += ta[q].w;
+            b.x += tb[q].x; b.y += tb[q].y; b.z += tb[q].z; b.w += tb[q].w;
+        }
+        if (p.fold.bias) {
+            const float4 ba = *reinterpret_cast<const float4*>(p.fold.bias + col + i0), bb = *reinterpret_cast<const float4*>(p.fold.bias + col + half + i0);
+            a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+            b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
+        }
+    } else {
+        a = qkv_at4(p, t, col + i0); b = qkv_at4(p, t, col + half + i0);
+    }
+    ra = a; rb = b;
+    if (rotate && p.table) {
+        const float4 c01 = *reinterpret_cast<const float4*>(p.table + (long long)t * half + i0);
+        const float4 c23 = *reinterpret_cast<const float4*>(p.table + (long long)t * half + i0 + 2);
+        ra.x = a.x * c01.x - b.x * c01.y; rb.x = a.x * c01.y + b.x * c01.x;
+        ra.y = a.y * c01.z - b.y * c01.w; rb.y = a.y * c01.w + b.y * c01.z;
+        ra.z = a.z * c23.x - b.z * c23.y; rb.z = a.z * c23.y + b.z * c23.x;
+        ra.w = a.w * c23.z - b.w * c23.w; rb.w = a.w * c23.w + b.w * c23.z;
+    }
+}
 
 template <int HD> struct Swz {
     static constexpr int CPR = HD / 8;  // 16-byte chunks per row
@@ -98,7 +152,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait_pending() {
 }
 
 template <int HD, bool DECODE>
-__global__ void __launch_bounds__(FA_THREADS, DECODE ? 1 : 3)     // prefill shape: three CTAs per SM
+__global__ void __launch_bounds__(FA_THREADS, 3)     // three CTAs per SM
 attention_fa_kernel(const FaParams p) {
     constexpr int BM = DECODE ? 16 : 64;
     constexpr int CPR = HD / 8;
@@ -146,16 +200,42 @@ attention_fa_kernel(const FaParams p) {
                 load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
             cp_async_commit();
         }
-        // the older tiles beyond those: into L2 (two threads per key: its K row and its V row)
-        for (int tile = t_begin + NST - 1; tile < t_end && (tile + 1) * FA_BN <= new_from; ++tile) {
-            const int r = threadIdx.x >> 1;
-            if (r < FA_BN) {
-                const __nv_bfloat16* row = p.pool + p.kv.row(slot, tile * FA_BN + r, kvh) + ((threadIdx.x & 1) ? p.kv.v_offset : 0);
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(HD * 2) : "memory");
-            }
-        }
+        // (asking for the tiles beyond those into L2 was measured: no gain at batch 8, a loss at 64)
         pdl_wait();
     }
+    if (DECODE && p.qkv != nullptr) {
+        constexpr int HALF = HD / 2, QUADS = HD / 8;
+        const int q_dim = p.heads * HD, kv_dim = p.kv.kv_heads * HD;
+        // new keys and values: by the one CTA whose tiles hold the new positions, into the cache
+        // (later steps read them there) before its own loads of those tiles are issued
+        if (p.write_kv && t_begin * FA_BN < kv_hi && kv_hi <= t_end * FA_BN) {
+            for (int e = threadIdx.x; e < ntok * 2 * QUADS; e += FA_THREADS) {
+                const int j = e / (2 * QUADS), is_v = (e / QUADS) & 1, i0 = (e % QUADS) * 4;
+                float4 ra, rb;
+                rotated_quads(p, q_start + tok0 + j, q_dim + (is_v ? kv_dim : 0) + kvh * HD, HALF, i0, !is_v, ra, rb);
+                __nv_bfloat16* dst = p.pool_rw + p.kv.row(slot, pos0 + j, kvh) + (is_v ? p.kv.v_offset : 0);
+                *reinterpret_cast<uint2*>(dst + i0) = make_uint2(pack_bf16(ra.x, ra.y), pack_bf16(ra.z, ra.w));
+                *reinterpret_cast<uint2*>(dst + HALF + i0) = make_uint2(pack_bf16(rb.x, rb.y), pack_bf16(rb.z, rb.w));
+            }
+            __threadfence();
+        }
+        // this CTA's queries, rotated, straight into their shared-memory tile
+        for (int e = threadIdx.x; e < BM * QUADS; e += FA_THREADS) {
+            const int r = e / QUADS, i0 = (e % QUADS) * 4;
+            const uint32_t lo = q_sm + Swz<HD>::off(r, i0 >> 3) + (i0 & 4) * 2;
+            const uint32_t hi = q_sm + Swz<HD>::off(r, (HALF + i0) >> 3) + ((HALF + i0) & 4) * 2;
+            uint2 va = make_uint2(0u, 0u), vb = make_uint2(0u, 0u);
+            if (r < rows_used) {
+                float4 ra, rb;
+                rotated_quads(p, q_start + tok0 + r / p.group, (kvh * p.group + r % p.group) * HD, HALF, i0, true, ra, rb);
+                va = make_uint2(pack_bf16(ra.x, ra.y), pack_bf16(ra.z, ra.w));
+                vb = make_uint2(pack_bf16(rb.x, rb.y), pack_bf16(rb.z, rb.w));
+            }
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(lo), "r"(va.x), "r"(va.y) : "memory");
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(hi), "r"(vb.x), "r"(vb.y) : "memory");
+        }
+        __syncthreads();          // the new keys and values are in memory before any thread asks for their tile
+    } else
     // ---- Q tile -> shared (rows beyond rows_used are zero)
     for (int e = threadIdx.x; e < BM * CPR; e += FA_THREADS) {
         const int r = e / CPR, c = e % CPR;
@@ -642,10 +722,19 @@ AXON_API long long axon_attention_fa_scratch_floats(int n_items, int kv_heads, i
 // the split that finishes last folds the partials itself, without them a second kernel does.
 // tokens_per_tile * group rows must fit the tile.  scratch: see above (may be null when
 // n_splits == 1).  Head sizes 16, 32, 64, 128; group <= 16 (decode) or 64 (prefill).
-AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
+namespace {
+struct FusedQkv {            // see FaParams::qkv
+    const float* qkv = nullptr;
+    SplitFold fold{nullptr, nullptr, 0, 0};
+    const float2* table = nullptr;
+    int qkv_width = 0, write_kv = 0;
+};
+}
+
+static int attention_fa_launch(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
                                const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
                                float scale, int window, int decode, int tokens_per_tile, int n_splits,
-                               float* scratch, unsigned int* counters, cudaStream_t stream) {
+                               float* scratch, unsigned int* counters, const FusedQkv& fused, cudaStream_t stream) {
     if (n_items <= 0) return AXON_OK;
     const int hd = layout->head_dim, kvh = layout->kv_heads;
     if (heads % kvh) { set_error("axon_attention_fa: %d heads over %d kv heads", heads, kvh); return AXON_BAD_ARGUMENT; }
@@ -669,6 +758,8 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile;
     p.n_splits = n_splits; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.qkv = fused.qkv; p.fold = fused.fold; p.table = fused.table; p.pool_rw = (__nv_bfloat16*)const_cast<void*>(pool);
+    p.qkv_width = fused.qkv_width; p.write_kv = fused.write_kv;
 #define AXON_FA_CASE(HD)                                                                         \
     case HD: return decode ? launch_fa<HD, true>(p, n_items, kvh, stream) : launch_fa<HD, false>(p, n_items, kvh, stream);
     switch (hd) {
@@ -679,6 +770,41 @@ AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const
         default: set_error("axon_attention_fa: head size %d is not 16, 32, 64 or 128", hd); return AXON_BAD_ARGUMENT;
     }
 #undef AXON_FA_CASE
+}
+
+AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
+                               const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
+                               float scale, int window, int decode, int tokens_per_tile, int n_splits,
+                               float* scratch, unsigned int* counters, cudaStream_t stream) {
+    return attention_fa_launch(q, pool, out, segments, n_segments, items, n_items, layout, heads, scale, window, decode,
+                               tokens_per_tile, n_splits, scratch, counters, FusedQkv{}, stream);
+}
+
+// Decode steps (every segment at most `tokens_per_tile` tokens, segment i is item i): rotation,
+// cache write and attention in one kernel.  qkv: float [tokens][(heads + 2 kv_heads) * hd] with
+// biases added, or (partial != null) still owed the partial sums of a deferred split-K product
+// with its bias.  table: (cos, sin) [tokens][hd / 2] for pairs (i, i + hd / 2) over the whole
+// head, or null for no rotation.  write_kv == 0: the cache holds the new positions already
+// (a layer reading another layer's cache).  Otherwise as axon_attention_fa with decode != 0.
+AXON_API int axon_attention_fa_decode_fused(const float* qkv, const float* partial, int fold_splits, int fold_ntok,
+                                            const float* bias, const float* table, int write_kv, void* pool, void* out,
+                                            const int32_t* segments, int n_segments, const AxonKvLayoutFa* layout,
+                                            int heads, float scale, int window, int tokens_per_tile, int n_splits,
+                                            float* scratch, unsigned int* counters, cudaStream_t stream) {
+    const int hd = layout->head_dim;
+    if (qkv == nullptr) { set_error("axon_attention_fa_decode_fused: no q/k/v product given"); return AXON_BAD_ARGUMENT; }
+    if (hd % 8) { set_error("axon_attention_fa_decode_fused: head size %d is not a multiple of 8", hd); return AXON_BAD_ARGUMENT; }
+    if (partial != nullptr && (fold_splits < 1 || fold_ntok < 1)) { set_error("axon_attention_fa_decode_fused: bad partial sums"); return AXON_BAD_ARGUMENT; }
+    if (((uintptr_t)qkv | (uintptr_t)partial | (uintptr_t)bias | (uintptr_t)table) & 15) { set_error("axon_attention_fa_decode_fused: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
+    if ((layout->page_stride * 2) % 16 || (layout->entry_offset * 2) % 16 || (layout->v_offset * 2) % 16) { set_error("axon_attention_fa_decode_fused: cache planes must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
+    FusedQkv f;
+    f.qkv = qkv;
+    f.fold = SplitFold{partial, partial ? bias : nullptr, fold_splits, fold_ntok};
+    f.table = (const float2*)table;
+    f.qkv_width = (heads + 2 * layout->kv_heads) * hd;
+    f.write_kv = write_kv;
+    return attention_fa_launch(qkv, pool, out, segments, n_segments, nullptr, n_segments, layout, heads, scale, window, 1,
+                               tokens_per_tile, n_splits, scratch, counters, f, stream);
 }
 
 // ---------------------------------------------------------------------------

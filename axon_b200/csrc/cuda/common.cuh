@@ -79,17 +79,19 @@ struct SplitFold {
     const float* bias;
     int splits, ntok;
 
+    // All loads of a round of eight slabs are issued before the first is used: a reader pays one
+    // trip to L2 for them, not one per slab (missing slabs add zeros, which changes nothing).
     __device__ __forceinline__ float at(int token, int n) const {
         const float* p = partial + ((long long)(n >> 7) * splits * ntok + token) * 128 + (n & 127);
         const long long step = (long long)ntok * 128;
         float v = 0.f;
-        int s = 0;
-        for (; s + 4 <= splits; s += 4) {
-            const float t0 = __ldcg(p + s * step), t1 = __ldcg(p + (s + 1) * step);
-            const float t2 = __ldcg(p + (s + 2) * step), t3 = __ldcg(p + (s + 3) * step);
-            v += t0; v += t1; v += t2; v += t3;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) t[q] = s0 + q < splits ? __ldcg(p + (s0 + q) * step) : 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v += t[q];
         }
-        for (; s < splits; ++s) v += __ldcg(p + s * step);
         if (bias) v += bias[n];
         return v;
     }
@@ -98,18 +100,12 @@ struct SplitFold {
         const float4* p = reinterpret_cast<const float4*>(partial + ((long long)(n >> 7) * splits * ntok + token) * 128 + (n & 127));
         const long long step = (long long)ntok * 32;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        int s = 0;
-        for (; s + 4 <= splits; s += 4) {
-            const float4 t0 = __ldcg(p + s * step), t1 = __ldcg(p + (s + 1) * step);
-            const float4 t2 = __ldcg(p + (s + 2) * step), t3 = __ldcg(p + (s + 3) * step);
-            v.x += t0.x; v.y += t0.y; v.z += t0.z; v.w += t0.w;
-            v.x += t1.x; v.y += t1.y; v.z += t1.z; v.w += t1.w;
-            v.x += t2.x; v.y += t2.y; v.z += t2.z; v.w += t2.w;
-            v.x += t3.x; v.y += t3.y; v.z += t3.z; v.w += t3.w;
-        }
-        for (; s < splits; ++s) {
-            const float4 t = __ldcg(p + s * step);
-            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float4 t[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) t[q] = s0 + q < splits ? __ldcg(p + (s0 + q) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) { v.x += t[q].x; v.y += t[q].y; v.z += t[q].z; v.w += t[q].w; }
         }
         if (bias) {
             const float4 b = *reinterpret_cast<const float4*>(bias + n);

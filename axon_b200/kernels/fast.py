@@ -21,7 +21,7 @@ SMALL_M = 64
 
 #: switches for tests that compare a tuned kernel with the plain one
 ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attention_prefill": True,
-           "attention_decode": True, "attention_tc": True}
+           "attention_decode": True, "attention_tc": True, "attention_fused": True}
 
 
 def _stream() -> int:
@@ -213,6 +213,62 @@ def _attention_items(ctx, group: int, pre_rows: int = 64):
     return got
 
 
+def _decode_splits(n_dec: int, kv, tiles: int, rt):
+    """Key splits for the decode shape and the scratch their partials go to (None: a cluster folds)."""
+    # small batches: about two CTAs per SM; large ones (a CTA per request and kv head fills
+    # the machine already) still gain from three or four shares of the keys
+    target = FA_TARGET_CTAS if n_dec * kv.kv_heads < SM_COUNT else 2 * FA_TARGET_CTAS
+    splits = max(1, min(tiles, FA_MAX_SPLITS, -(-target // (n_dec * kv.kv_heads))))
+    scratch = None
+    # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
+    # no second kernel); longer contexts keep more, independent splits
+    if FA_CLUSTER and splits > 1 and -(-tiles // min(splits, 8)) <= 16:
+        splits = min(splits, 8)
+    elif splits > 1:
+        # sized for the most splits this batch can get, so that the buffer never moves
+        # while the contexts grow (captured graphs hold its address)
+        most = min(FA_MAX_SPLITS, -(-target // (n_dec * kv.kv_heads)))
+        scratch = rt.buffer("fa_scratch", (n_dec * kv.kv_heads * most * 16 * (kv.head_dim + 2),), torch.float32)
+    return splits, scratch
+
+
+def attention_decode_fused(qkv, pending, table, rot: int, adjacent: bool, kv, ctx, out, heads: int, scale: float,
+                           write_kv: bool) -> bool:
+    """Rotation, cache write and attention of a step of single tokens in one kernel: reads
+    the q/k/v product (or the partial sums it is still owed) instead of rotated queries.
+    Refuses what ``attention`` refuses, steps with prompt portions, partial or adjacent-pair
+    rotation, and head sizes that are no multiple of 8; the caller then takes the two kernels."""
+    if not (ENABLED["attention_decode"] and ENABLED["attention_fused"]) or ctx.unit_items is None:
+        return False
+    if out.dtype != torch.bfloat16 or kv.pool.dtype != torch.bfloat16 or kv.head_dim not in FA_HEAD_DIMS:
+        return False
+    if heads % kv.kv_heads or heads // kv.kv_heads > 16 or ctx.segments is None or qkv.dtype != torch.float32:
+        return False
+    if table is not None and (adjacent or rot != kv.head_dim):
+        return False
+    if not qkv.is_contiguous() or (table is not None and not table.is_contiguous()):
+        return False
+    n = len(ctx.seg_slot)
+    tiles = -(-ctx.max_kv_len // 64)
+    splits, scratch = _decode_splits(n, kv, tiles, ctx.rt)
+    # every CTA rotates its own queries: worth it while all CTAs run at once (three per SM);
+    # beyond that the separate rotation kernel is cheaper (measured at batch 64: 15 % of the step)
+    if n * kv.kv_heads * splits > 3 * SM_COUNT:
+        return False
+    counters = _split_scratch(qkv.device)[2]
+    if pending is not None:
+        pending.claim(qkv, accumulate=False)
+    check(lib.cuda().axon_attention_fa_decode_fused(
+        qkv.data_ptr(), None if pending is None else pending.partial.data_ptr(),
+        0 if pending is None else pending.splits, 0 if pending is None else pending.ntok,
+        None if pending is None or pending.bias is None else pending.bias.data_ptr(),
+        None if table is None else table.data_ptr(), int(write_kv), kv.pool.data_ptr(), out.data_ptr(),
+        ctx.segments.data_ptr(), n, kv._ref, heads, float(scale), int(kv.window), 16 // (heads // kv.kv_heads), splits,
+        None if scratch is None else scratch.data_ptr(),
+        counters.data_ptr() if FA_FOLD_IN_KERNEL and n * kv.kv_heads <= counters.numel() else None, _stream()))
+    return True
+
+
 def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     """Tensor-core attention over the paged cache; refuses head sizes other than
     16/32/64/128, groups of more than 64 heads, and dtypes other than bfloat16."""
@@ -230,22 +286,8 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     n_seg = len(ctx.seg_slot)
     if it["n_dec"]:
         tiles = -(-it["dec_kv"] // 64)
-        # small batches: about two CTAs per SM; large ones (a CTA per request and kv head fills
-        # the machine already) still gain from three or four shares of the keys
-        target = FA_TARGET_CTAS if it["n_dec"] * kv.kv_heads < SM_COUNT else 2 * FA_TARGET_CTAS
-        splits = max(1, min(tiles, FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads))))
-        scratch = None
+        splits, scratch = _decode_splits(it["n_dec"], kv, tiles, ctx.rt)
         counters = _split_scratch(q.device)[2]
-        # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
-        # no second kernel); longer contexts keep more, independent splits
-        if FA_CLUSTER and splits > 1 and -(-tiles // min(splits, 8)) <= 16:
-            splits = min(splits, 8)
-        elif splits > 1:
-            # sized for the most splits this batch can get, so that the buffer never moves
-            # while the contexts grow (captured graphs hold its address)
-            most = min(FA_MAX_SPLITS, -(-target // (it["n_dec"] * kv.kv_heads)))
-            scratch = ctx.rt.buffer("fa_scratch", (it["n_dec"] * kv.kv_heads * most * 16 * (kv.head_dim + 2),),
-                                    torch.float32)
         check(cu.axon_attention_fa(q.data_ptr(), kv.pool.data_ptr(), out.data_ptr(), ctx.segments.data_ptr(), n_seg,
                                    None if it["dec"] is None else it["dec"].data_ptr(), it["n_dec"], kv._ref, heads,
                                    float(scale), int(kv.window),

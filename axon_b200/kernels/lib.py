@@ -62,6 +62,8 @@ _SIGNATURES = {
                            ctypes.POINTER(c_int), P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
+    "axon_attention_fa_decode_fused": [P, P, c_int, c_int, P, P, c_int, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int,
+                                       c_float, c_int, c_int, c_int, P, P, P],
     "axon_attention_tc": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int, P],
     "axon_attention_tc_status": [],
 }

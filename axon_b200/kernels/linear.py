@@ -51,3 +51,13 @@ def attention(q: torch.Tensor, kv: ops.KvView, ctx, out: torch.Tensor, heads: in
         if fast.attention(q, kv, ctx, out, heads, scale):
             return
     ops.attention_plain(q, kv, ctx.positions, ctx.token_slot, out, heads, scale)
+
+
+def attention_decode_fused(qkv: torch.Tensor, pending, table, rot: int, adjacent: bool, kv: ops.KvView, ctx,
+                           out: torch.Tensor, heads: int, scale: float, write_kv: bool, precise: bool = False) -> bool:
+    """One kernel for rotation, cache write and attention of a step of single tokens; False when
+    the sizes (or the 32-bit model) need the separate kernels, in which case nothing ran."""
+    if precise:
+        return False
+    from . import fast
+    return fast.attention_decode_fused(qkv, pending, table, rot, adjacent, kv, ctx, out, heads, scale, write_kv)

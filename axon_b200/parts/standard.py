@@ -154,11 +154,14 @@ class Attention(Mixer):
         table, rot, adjacent = None, 0, False
         if self.position is not None:
             table, rot, adjacent = self.position.rotation(ctx), self.position.rot, self.position.adjacent
-        q = rt.buffer("q", (n, self.q_dim))
-        ops.rope_kv_write(qkv, table, ctx.positions, ctx.token_slot, q, cache, self.heads, rot, adjacent,
-                          write_kv=write_cache, pending=owed)
         att = rt.buffer("att", (n, self.q_dim))
-        _linear.attention(q, cache, ctx, att, self.heads, self.scale, precise=rt.precise)
+        # steps of single tokens: rotation, cache write and attention in one kernel
+        if not _linear.attention_decode_fused(qkv, owed, table, rot, adjacent, cache, ctx, att, self.heads, self.scale,
+                                              write_cache, precise=rt.precise):
+            q = rt.buffer("q", (n, self.q_dim))
+            ops.rope_kv_write(qkv, table, ctx.positions, ctx.token_slot, q, cache, self.heads, rot, adjacent,
+                              write_kv=write_cache, pending=owed)
+            _linear.attention(q, cache, ctx, att, self.heads, self.scale, precise=rt.precise)
         return _linear.linear(att, self.w_o, x, bias=self.b_o, accumulate=True, precise=rt.precise, defer=defer)
 
 

@@ -664,6 +664,56 @@ def test_attention_tcgen05_prompts(ops, heads, kv_heads, ps, window, shapes):
         at += n
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd,ps,window,split_product", [
+    (28, 4, 128, 16, 0, True), (6, 2, 64, 8, 0, False), (8, 8, 128, 16, 40, True), (4, 1, 32, 4, 0, True),
+    (16, 1, 16, 16, 0, False)])
+def test_decode_attention_rotates_and_writes_by_itself(ops, heads, kv_heads, hd, ps, window, split_product):
+    """A step of single tokens: the kernel that rotates the queries, writes the new keys and values
+    and attends, against the rotation kernel followed by the attention kernel.  Same bits out, same
+    cache; also when the q/k/v product is still owed its partial sums, and when the cache is only read."""
+    from axon_b200.kernels import fast
+    from axon_b200.parts import Runtime, StepContext
+    kv_lens = [1, 64, 65, 700, 129, 2]
+    n, width = len(kv_lens), (heads + 2 * kv_heads) * hd
+    K = 2048 if split_product else 64
+    a = rand(n, K, dtype=torch.bfloat16, seed=130)
+    w = rand(width, K, dtype=torch.bfloat16, seed=131, std=0.05 if split_product else 0.3)
+    bias = rand(width, seed=132)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    positions, slots = i32([k - 1 for k in kv_lens]), i32(list(range(n)))
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    table = torch.empty(n, hd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions, inv.to(DEV), table)
+    rows = [list(range(n)), list(range(n)), [1] * n, kv_lens]
+    results = []
+    for fused in (False, True):
+        for write_kv in (True, False):
+            view, tbl = make_cache(ops, torch.bfloat16, kv_heads, hd, ps, n * -(-704 // ps), n, 704, window=window, seed=17)
+            view.pool.copy_(rand(*view.pool.shape, dtype=torch.bfloat16, seed=133))     # older keys and values
+            ctx = StepContext(rt=Runtime(torch.bfloat16, DEV), n_tokens=n, tokens=i32([0] * n), positions=positions,
+                              token_slot=slots, seg_slot=rows[0], seg_q_start=rows[1], seg_q_len=rows[2],
+                              seg_kv_len=rows[3], segments=i32(rows), unit_items=i32([[s, 0] for s in range(n)]).flatten(),
+                              host_positions=[k - 1 for k in kv_lens])
+            qkv = torch.zeros(n, width, dtype=torch.float32, device=DEV)
+            owed = fast.gemm(a, w, qkv, bias, False, defer=True)
+            assert isinstance(owed, fast.PendingFold) == split_product
+            owed = owed if split_product else None
+            out = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+            scale = 1.0 / math.sqrt(hd)
+            if fused:
+                assert fast.attention_decode_fused(qkv, owed, table, hd, False, view, ctx, out, heads, scale, write_kv)
+            else:
+                q = torch.zeros(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+                ops.rope_kv_write(qkv, table, positions, slots, q, view, heads, hd, write_kv=write_kv, pending=owed)
+                assert fast.attention(q, view, ctx, out, heads, scale)
+            results.append((out, view.pool.clone()))
+    for (o_two, c_two), (o_one, c_one) in zip(results[:2], results[2:]):
+        assert torch.equal(c_two, c_one), "the caches differ"
+        assert torch.equal(o_two, o_one), "the outputs differ"
+    assert not torch.equal(results[0][1], results[1][1]), "writing the cache changed nothing"
+    assert results[0][0].float().abs().sum() > 0
+
+
 def test_attention_tensor_core_refusals(ops):
     from axon_b200.kernels import fast
     view, _ = make_cache(ops, torch.bfloat16, 1, 48, 16, 4, 1, 64)
