@@ -116,7 +116,8 @@ def _build(name: str, out: str, sources: List[str], headers: List[str], compile_
         if os.path.exists(out) and os.path.exists(stamp) and open(stamp).read().strip() == want:
             return out
         t0 = time.time()
-        _say(f"{name}: compiling {len(sources)} source files for sm_100a (first use of this checkout)")
+        what = "for sm_100a " if any(x.endswith(".cu") for x in sources) else ""
+        _say(f"{name}: compiling {len(sources)} source files {what}(first use of this checkout, or its sources changed)")
         objs = []
         with _Heartbeat(name), concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
             futs = {}
