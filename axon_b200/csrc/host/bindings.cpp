@@ -71,6 +71,18 @@ PYBIND11_MODULE(axon_host, m) {
         .def("could_ever_hold", &CacheManager::could_ever_hold)
         .def("version", &CacheManager::version)
         .def("check", &CacheManager::check)
+        // a step of single tokens laid out in one call; see cache_manager.h
+        .def("stage_decode", [](CacheManager& c, const std::vector<int>& slots, const std::vector<int>& tokens,
+                                const std::vector<unsigned char>& wanted, int vocab,
+                                py::array_t<int32_t, py::array::c_style> out) {
+            const int n = (int)slots.size();
+            if (tokens.size() != slots.size() || wanted.size() != slots.size()) throw CacheError("stage_decode: lists of different lengths");
+            if (out.size() < (py::ssize_t)(10 * (size_t)n)) throw CacheError("stage_decode: the output block is too small");
+            int bad = -1;
+            const int rc = c.stage_decode(slots.data(), tokens.data(), wanted.data(), n, vocab, out.mutable_data(), &bad);
+            return py::make_tuple(rc, bad);
+        })
+        .def("commit_decode", [](CacheManager& c, const std::vector<int>& slots) { c.commit_decode(slots.data(), (int)slots.size()); })
         // the host block table of a group as a numpy view [max_slots][stride] (no copy)
         .def("table", [](CacheManager& c, int g) {
             return py::array_t<int32_t>({(py::ssize_t)c.max_slots(), (py::ssize_t)c.table_stride(g)},

@@ -216,6 +216,40 @@ void CacheManager::flush() {
     for (auto& a : allocs_) a.flush();
 }
 
+int CacheManager::stage_decode(const int* slots, const int* tokens, const unsigned char* wanted, int n, int vocab,
+                               int32_t* out, int* bad) {
+    *bad = -1;
+    if (n <= 0) return 1;
+    stage_seen_.assign((size_t)max_slots_, 0);
+    for (int i = 0; i < n; ++i) {
+        const int s = slots[i];
+        if (s < 0 || s >= max_slots_ || !is_open(s) || stage_seen_[s]) return 1;
+        stage_seen_[s] = 1;
+        if (tokens[i] < 0 || tokens[i] >= vocab) return 1;
+        if (slots_[s].length + 1 > max_positions_) return 1;
+    }
+    flush();
+    for (int i = 0; i < n; ++i) {
+        if (!reserve(slots[i], slots_[slots[i]].length + 1)) { *bad = i; return 2; }
+    }
+    int32_t* tok = out; int32_t* pos = out + n; int32_t* sl = out + 2 * n; int32_t* seg = out + 3 * n;
+    int32_t* want = out + 7 * n;
+    int n_want = 0;
+    for (int i = 0; i < n; ++i) {
+        const int start = slots_[slots[i]].length;
+        tok[i] = tokens[i]; pos[i] = start; sl[i] = slots[i];
+        seg[i] = slots[i]; seg[n + i] = i; seg[2 * n + i] = 1; seg[3 * n + i] = start + 1;
+        if (wanted[i]) want[n_want++] = i;
+    }
+    int32_t* items = want + n_want;
+    for (int i = 0; i < n; ++i) { items[2 * i] = i; items[2 * i + 1] = 0; }
+    return 0;
+}
+
+void CacheManager::commit_decode(const int* slots, int n) {
+    for (int i = 0; i < n; ++i) commit(slots[i], slots_[slots[i]].length + 1);
+}
+
 int CacheManager::slot_pages(int g, int slot) const {
     if (!is_open(slot)) return 0;
     const Slot& sl = slots_[slot];

@@ -86,6 +86,18 @@ public:
     // Retired pages become free.
     void flush();
 
+    // A step of one token for each of `n` requests, laid out for the device in one call (what the
+    // step function otherwise does entry by entry): checks the slots (open, distinct), the tokens
+    // (0 <= t < vocab) and the context limit, flushes, takes the pages, and fills `out`:
+    //   tokens[n] positions[n] slots[n] segments[4][n] (slot, q_start, 1, kv_len) wanted rows[n_want]
+    //   items[n][2] (segment, 0)
+    // wanted[i] != 0 asks for request i's logits.  Returns 0; 1 when the input is irregular (nothing
+    // is taken; the caller's own checks find the words for it); 2 when request *bad has no pages.
+    int stage_decode(const int* slots, const int* tokens, const unsigned char* wanted, int n, int vocab,
+                     int32_t* out, int* bad);
+    // The lengths of those requests grow by one.
+    void commit_decode(const int* slots, int n);
+
     int free_pages(int g) const { return allocs_.at(g).n_free(); }
     int retired_pages(int g) const { return allocs_.at(g).n_retired(); }
     int held_pages(int g) const { return allocs_.at(g).n_held(); }
@@ -121,6 +133,7 @@ private:
     int logical_pages(int g, int positions) const;
     int first_needed(int g, int next_query_pos) const;
 
+    std::vector<unsigned char> stage_seen_;   // scratch of stage_decode
     std::vector<GroupConfig> groups_;
     int max_slots_, max_positions_;
     std::vector<PageAllocator> allocs_;

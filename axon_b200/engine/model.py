@@ -65,6 +65,9 @@ class DecoderModel:
         """Run the step's tokens through every schedule entry; the float32 logits of
         the wanted rows ``[n_want, vocab]`` (None when nothing is wanted)."""
         rt, n = self.rt, ctx.n_tokens
+        if not rt.precise:
+            from ..kernels import fast
+            fast.forget_owed(rt.device)      # whatever a step that failed half way still owed is void
         x = rt.buffer("residual", (n, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx.tokens, x)
         owed = None          # partial sums the residual is still owed by the last product into it

@@ -92,6 +92,9 @@ class Engine:
         cache, vocab = self.cache, self.model.spec.vocab_size
         if not entries:
             return None
+        staged = self._stage_single_tokens(entries)
+        if staged is not None:
+            return self._run(*staged)
         seen = set()
         n = 0
         for e in entries:
@@ -157,6 +160,42 @@ class Engine:
             items[:, 0] = np.arange(s, dtype=np.int32)
             items[:, 1] = 0
 
+        return self._run(entries, starts, stage, total, n, s, n_want, decode_only, seg_slot, seg_q_start, seg_q_len,
+                         seg_kv_len, positions.tolist())
+
+    def _stage_single_tokens(self, entries: Sequence[StepEntry]):
+        """A step of one token per request, checked and laid out by the cache manager in one call
+        (the host's share of such a step is otherwise about 10 us a request, which nothing hides).
+        None when the step is not of that kind or something about it is irregular: the general
+        path then finds the words for it."""
+        s = len(entries)
+        slots, toks, wanted = [], [], []
+        for e in entries:
+            if len(e.tokens) != 1:
+                return None
+            w = e.want
+            if len(w) > 1 or (len(w) == 1 and w[0] != 0):
+                return None
+            slots.append(e.slot); toks.append(e.tokens[0]); wanted.append(len(w))
+        n_want = sum(wanted)
+        total = 9 * s + n_want
+        stage = self._stage(total)
+        try:
+            rc, _ = self.cache.manager.stage_decode(slots, toks, wanted, self.model.spec.vocab_size, stage.numpy())
+        except (TypeError, ValueError, OverflowError):
+            rc = 1                                   # ids that are no plain integers
+        if rc != 0:
+            self._turn ^= 1                          # the staging buffer was not used
+            return None
+        buf = stage.numpy()
+        starts = buf[s:2 * s].tolist()
+        return (entries, starts, stage, total, s, s, n_want, True, slots, list(range(s)), [1] * s,
+                buf[6 * s:7 * s].tolist(), starts)
+
+    def _run(self, entries, starts, stage, total, n, s, n_want, decode_only, seg_slot, seg_q_start, seg_q_len,
+             seg_kv_len, host_positions) -> Optional[torch.Tensor]:
+        """Copy the staged step to the device, run the model, commit the new lengths."""
+        cache = self.cache
         # A decode-only step of a shape seen before replays a captured CUDA graph: every
         # kernel argument that depends on the host is in the key, everything else
         # (tokens, positions, slots, lengths, block tables) is read from device memory.
@@ -177,15 +216,18 @@ class Engine:
                 seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len,
                 segments=dev[3 * n:3 * n + 4 * s].view(4, s),
                 unit_items=dev[total - 2 * s: total] if decode_only else None,
-                host_positions=positions.tolist())
+                host_positions=host_positions)
         want_rows = dev[3 * n + 4 * s: 3 * n + 4 * s + n_want] if n_want else None
 
         if graph_key is None:
             logits = self.model.forward(context(), cache, want_rows, n_want)
         else:
             logits = self._graph_step(graph_key, context, want_rows, n_want)
-        for e, start in zip(entries, starts):
-            cache.commit(e.slot, start + len(e.tokens))
+        if decode_only and seg_q_len == [1] * s:
+            cache.manager.commit_decode(seg_slot)
+        else:
+            for e, start in zip(entries, starts):
+                cache.commit(e.slot, start + len(e.tokens))
         self.steps += 1
         return logits
 

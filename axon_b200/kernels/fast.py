@@ -71,6 +71,15 @@ class PendingFold:
 
 
 _OUTSTANDING = {}
+
+
+def forget_owed(device: torch.device) -> None:
+    """Drop the record of partial sums nobody claimed (a step that failed half way leaves one)."""
+    device = torch.device(device)
+    for k in list(_OUTSTANDING):
+        if k.type == device.type and (device.index is None or k.index == device.index):
+            _OUTSTANDING[k] = None
+
 #: whether products for few rows may leave their partial sums to the reader of the output
 DEFER_FOLD = os.environ.get("AXON_DEFER_FOLD", "1") != "0"
 

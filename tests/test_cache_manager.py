@@ -144,3 +144,47 @@ def test_slots_are_reused_and_limited(host):
     with pytest.raises(host.CacheError, match="exceeds"):
         m.reserve(b, 17)
     assert m.could_ever_hold(16) and not m.could_ever_hold(17)
+
+
+def test_staged_decode_step_matches_the_calls_it_replaces(host):
+    """stage_decode checks, reserves and lays out a step of single tokens in one call; the layout and
+    the manager's state are what reserve/commit entry by entry give, and irregular input takes nothing."""
+    def fresh():
+        m = host.CacheManager([host.GroupConfig(4, 12)], max_slots=4, max_positions=64)
+        slots = [m.open_slot() for _ in range(3)]
+        for s, n in zip(slots, (3, 4, 8)):
+            assert m.reserve(s, n)
+            m.commit(s, n)
+        return m, slots
+    m, slots = fresh()
+    out = np.full(64, -7, dtype=np.int32)
+    rc, bad = m.stage_decode(slots, [5, 6, 7], [1, 0, 1], 100, out)
+    assert (rc, bad) == (0, -1)
+    n = 3
+    assert out[0:n].tolist() == [5, 6, 7] and out[n:2 * n].tolist() == [3, 4, 8] and out[2 * n:3 * n].tolist() == slots
+    assert out[3 * n:7 * n].reshape(4, n).tolist() == [slots, [0, 1, 2], [1, 1, 1], [4, 5, 9]]
+    assert out[7 * n:7 * n + 2].tolist() == [0, 2]                      # wanted rows
+    assert out[7 * n + 2:7 * n + 2 + 2 * n].tolist() == [0, 0, 1, 0, 2, 0]  # work items
+    assert [m.reserved_length(s) for s in slots] == [4, 5, 9]
+    m.commit_decode(slots)
+    assert [m.length(s) for s in slots] == [4, 5, 9]
+    m.check()
+    # the same through the single calls
+    m2, slots2 = fresh()
+    for s in slots2:
+        assert m2.reserve(s, m2.length(s) + 1)
+    for s in slots2:
+        m2.commit(s, m2.length(s) + 1)
+    assert [m2.length(s) for s in slots2] == [4, 5, 9] and m2.free_pages(0) == m.free_pages(0)
+    # irregular input: nothing is taken
+    for bad_slots, toks in (([slots[0], slots[0]], [1, 1]), ([slots[0], 3], [1, 1]), ([slots[0]], [100]), ([slots[0]], [-1])):
+        free = m.free_pages(0)
+        rc, _ = m.stage_decode(bad_slots, toks, [1] * len(toks), 100, out)
+        assert rc == 1 and m.free_pages(0) == free
+    # no pages: says which request
+    m3 = host.CacheManager([host.GroupConfig(4, 3)], max_slots=4, max_positions=64)
+    a, b = m3.open_slot(), m3.open_slot()
+    assert m3.reserve(a, 4) and m3.reserve(b, 8)
+    m3.commit(a, 4); m3.commit(b, 8)
+    rc, bad = m3.stage_decode([a, b], [1, 1], [1, 1], 100, out)
+    assert (rc, bad) == (2, 0)
