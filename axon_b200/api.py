@@ -253,9 +253,7 @@ class Backend:
         host integers (the batch form of ``forward_argmax``)."""
         if len(tokens) != len(caches):
             raise StepError("decode_batch needs one token per cache")
-        logits = self.engine.step([StepEntry(c.slot, [int(t)], [0]) for c, t in zip(caches, tokens)])
-        best = torch.empty(len(caches), dtype=torch.int32, device=logits.device)
-        ops.argmax(logits, best)
+        best = self.engine.step([StepEntry(c.slot, [int(t)], [0]) for c, t in zip(caches, tokens)], greedy=True)
         return best.tolist()
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], n_gen: Union[int, Sequence[int]],

@@ -88,13 +88,17 @@ class Engine:
         self._cur = i
         return self._staging[i]
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False) -> Optional[torch.Tensor]:
+        """Run the entries' tokens; the float32 logits at the wanted places, ``[wanted, vocab]``.
+        With ``greedy`` the largest logit of each wanted place is picked on the device in the same
+        launch (the same CUDA graph for steps of single tokens) and the int32 ids come back instead.
+        Both live in buffers of the engine: valid until the next step."""
         cache, vocab = self.cache, self.model.spec.vocab_size
         if not entries:
             return None
         staged = self._stage_single_tokens(entries)
         if staged is not None:
-            return self._run(*staged)
+            return self._run(*staged, greedy=greedy)
         seen = set()
         n = 0
         for e in entries:
@@ -161,7 +165,7 @@ class Engine:
             items[:, 1] = 0
 
         return self._run(entries, starts, stage, total, n, s, n_want, decode_only, seg_slot, seg_q_start, seg_q_len,
-                         seg_kv_len, positions.tolist())
+                         seg_kv_len, positions.tolist(), greedy=greedy)
 
     def _stage_single_tokens(self, entries: Sequence[StepEntry]):
         """A step of one token per request, checked and laid out by the cache manager in one call
@@ -193,7 +197,7 @@ class Engine:
                 buf[6 * s:7 * s].tolist(), starts)
 
     def _run(self, entries, starts, stage, total, n, s, n_want, decode_only, seg_slot, seg_q_start, seg_q_len,
-             seg_kv_len, host_positions) -> Optional[torch.Tensor]:
+             seg_kv_len, host_positions, greedy: bool = False) -> Optional[torch.Tensor]:
         """Copy the staged step to the device, run the model, commit the new lengths."""
         cache = self.cache
         # A decode-only step of a shape seen before replays a captured CUDA graph: every
@@ -201,7 +205,7 @@ class Engine:
         # (tokens, positions, slots, lengths, block tables) is read from device memory.
         graph_key = None
         if self.cuda_graphs and decode_only and n <= self.graph_max_batch:
-            graph_key = (n, n_want, min(32, -(-max(seg_kv_len) // 64)))
+            graph_key = (n, n_want, min(32, -(-max(seg_kv_len) // 64)), bool(greedy))
         meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{graph_key[0]}_{graph_key[1]}"
         dev = self.rt.buffer(meta_name, (total,), torch.int32)
         dev.copy_(stage[:total], non_blocking=True)
@@ -221,8 +225,13 @@ class Engine:
 
         if graph_key is None:
             logits = self.model.forward(context(), cache, want_rows, n_want)
+            if greedy and logits is not None:
+                from ..kernels import ops
+                picks = self.rt.buffer("greedy_picks", (n_want,), torch.int32)
+                ops.argmax(logits, picks)
+                logits = picks
         else:
-            logits = self._graph_step(graph_key, context, want_rows, n_want)
+            logits = self._graph_step(graph_key, context, want_rows, n_want, greedy)
         if decode_only and seg_q_len == [1] * s:
             cache.manager.commit_decode(seg_slot)
         else:
@@ -231,27 +240,36 @@ class Engine:
         self.steps += 1
         return logits
 
-    def _graph_step(self, key, context, want_rows, n_want) -> Optional[torch.Tensor]:
+    def _graph_step(self, key, context, want_rows, n_want, greedy: bool = False) -> Optional[torch.Tensor]:
         """Run a decode-only step through its CUDA graph, capturing it the first time.
         The logits live in a buffer of the graph: they are valid until the next step."""
         if self._graph_generation != self.rt.generation:
             self._graphs.clear()              # a scratch buffer moved: captured addresses are stale
             self._graph_generation = self.rt.generation
         out = self.rt.buffer(f"graph_logits_{n_want}", (max(n_want, 1), self.model.spec.vocab_size), torch.float32)
+        picks = self.rt.buffer(f"graph_picks_{n_want}", (max(n_want, 1),), torch.int32) if greedy else None
+        result = (picks if greedy else out)[:n_want] if n_want else None
+
+        def run() -> None:
+            self.model.forward(context(), self.cache, want_rows, n_want, logits_out=out)
+            if greedy and n_want:
+                from ..kernels import ops
+                ops.argmax(out[:n_want], picks[:n_want])
+
         entry = self._graphs.get(key)
         if entry is not None:
             graph, launches = entry
             graph.replay()
             lib.add_launches(launches)
-            return out[:n_want] if n_want else None
+            return result
         # first time: run it plainly (this also sizes every scratch buffer), then record it
-        self.model.forward(context(), self.cache, want_rows, n_want, logits_out=out)
+        run()
         if self._graph_generation == self.rt.generation:
             try:
                 graph = torch.cuda.CUDAGraph()
                 before = lib.launch_count()
                 with torch.cuda.graph(graph):
-                    self.model.forward(context(), self.cache, want_rows, n_want, logits_out=out)
+                    run()
                 launches = lib.launch_count() - before
                 lib.add_launches(-launches)       # recorded, not run
                 if self._graph_generation == self.rt.generation:
@@ -263,4 +281,4 @@ class Engine:
                 self.cuda_graphs = False
         else:
             self._graph_generation = self.rt.generation
-        return out[:n_want] if n_want else None
+        return result

@@ -360,6 +360,26 @@ def test_step_refusals(model_folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_pick_inside_the_step(model_folders, dtype):
+    """``step(..., greedy=True)`` returns the ids that the argmax of the same step's logits gives,
+    for prompt portions (eager) and for steps of single tokens (the captured graph, replayed)."""
+    from axon_b200.engine.step import StepEntry
+    engine = build(model_folders["B"], dtype, max_tokens=512, page_size=16, max_slots=4)
+    a, b = engine.open_request(), engine.open_request()
+    prompt = tokens_for("B", 0, 21)
+    want = engine.step([StepEntry(a, prompt, [3, 20])]).argmax(dim=1).tolist()
+    got = engine.step([StepEntry(b, prompt, [3, 20])], greedy=True)
+    assert got.dtype == torch.int32 and got.tolist() == want
+    ta = tb = want[1]
+    for _ in range(6):        # the first such step captures the graph, the others replay it
+        ta = engine.step([StepEntry(a, [ta], [0])]).argmax(dim=1).tolist()[0]
+        tb = engine.step([StepEntry(b, [tb], [0])], greedy=True).tolist()[0]
+        assert ta == tb
+    both = engine.step([StepEntry(a, [ta], [0]), StepEntry(b, [tb], [])], greedy=True)
+    assert both.shape == (1,)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(model_folders, plain_models, tmp_path, dtype):
     """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and `done` lines out."""
     name = "B"
