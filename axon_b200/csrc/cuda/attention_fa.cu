@@ -130,29 +130,64 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Gather one 64-key tile of K and of V for kv head `kvh` into shared memory; a row's place
-// in its page is worked out once for both.
-template <int HD>
-__device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const __nv_bfloat16* pool,
-                                             const PagedKv& kv, int slot, int kvh, int key0, int kv_len) {
-    constexpr int CPR = HD / 8;
-    for (int e = threadIdx.x; e < FA_BN * CPR; e += FA_THREADS) {
-        const int r = e / CPR, c = e % CPR;
-        int pos = key0 + r;
-        // rows past the request's length read its last position: finite data, masked later
-        if (pos >= kv_len) pos = kv_len - 1;
-        const __nv_bfloat16* src = pool + kv.row(slot, pos, kvh) + c * 8;
-        const uint32_t off = Swz<HD>::off(r, c);
-        cp_async16(k_tile + off, src);
-        cp_async16(v_tile + off, src + kv.v_offset);
+// Gathers 64-key tiles of K and of V for one (request, kv head) into shared memory.  A thread
+// copies one 16-byte chunk of every RPP-th row.  When the page size divides 64 a row's page within
+// the tile and its place inside that page are the same for every tile, so they are worked out once
+// (the division by the page size per row and tile was a third of the decode kernel's instructions).
+template <int HD> struct KvLoader {
+    static constexpr int CPR = HD / 8, RPP = FA_THREADS / CPR, ITER = FA_BN / RPP;
+    const int32_t* bt;              // the request's row of the block table
+    const __nv_bfloat16* src0;      // this thread's chunk of row 0 of the kv head in page 0 (K plane)
+    long long page_stride, v_off;
+    int ps, pages_per_tile, last_page, kv_len, r0;
+    int in_page[ITER], page_of[ITER];
+    uint32_t dst[ITER];
+
+    __device__ __forceinline__ void init(const __nv_bfloat16* pool, const PagedKv& kv, int slot, int kvh, int kv_len_) {
+        const int c = threadIdx.x % CPR;
+        r0 = threadIdx.x / CPR;
+        ps = kv.page_size; kv_len = kv_len_;
+        bt = kv.block_table + (long long)slot * kv.table_stride;
+        src0 = pool + kv.entry_offset + (long long)kvh * ps * HD + c * 8;
+        page_stride = kv.page_stride; v_off = kv.v_offset;
+        pages_per_tile = FA_BN % ps == 0 ? FA_BN / ps : 0;
+        last_page = (kv_len - 1) / ps;
+#pragma unroll
+        for (int j = 0; j < ITER; ++j) {
+            const int r = r0 + RPP * j;
+            page_of[j] = r / ps;
+            in_page[j] = (r % ps) * HD;
+            dst[j] = Swz<HD>::off(r, c);
+        }
     }
-}
+    // rows past the request's length read its last page (fast path) or last position: finite data, masked later
+    __device__ __forceinline__ void load(uint32_t k_tile, uint32_t v_tile, int key0) const {
+        if (pages_per_tile) {
+            const int first = (key0 / FA_BN) * pages_per_tile;
+#pragma unroll
+            for (int j = 0; j < ITER; ++j) {
+                const int page = bt[min(first + page_of[j], last_page)];
+                const __nv_bfloat16* src = src0 + (long long)page * page_stride + in_page[j];
+                cp_async16(k_tile + dst[j], src);
+                cp_async16(v_tile + dst[j], src + v_off);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < ITER; ++j) {
+                const int pos = min(key0 + r0 + RPP * j, kv_len - 1), lp = pos / ps;
+                const __nv_bfloat16* src = src0 + (long long)bt[lp] * page_stride + (pos - lp * ps) * HD;
+                cp_async16(k_tile + dst[j], src);
+                cp_async16(v_tile + dst[j], src + v_off);
+            }
+        }
+    }
+};
 template <int N> __device__ __forceinline__ void cp_async_wait_pending() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 template <int HD, bool DECODE>
-__global__ void __launch_bounds__(FA_THREADS, 3)     // three CTAs per SM
+__global__ void __launch_bounds__(FA_THREADS, (DECODE || HD == 128) ? 2 : 3)   // as many CTAs as shared memory holds
 attention_fa_kernel(const FaParams p) {
     constexpr int BM = DECODE ? 16 : 64;
     constexpr int CPR = HD / 8;
@@ -192,12 +227,14 @@ attention_fa_kernel(const FaParams p) {
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi, t_begin + per);
 
     const int new_from = kv_len - q_len;              // the segment's first position written by this step
+    KvLoader<HD> loader;
+    loader.init(p.pool, p.kv, slot, kvh, kv_len);
     if (DECODE) {
 #pragma unroll
         for (int st = 0; st < NST - 1; ++st) {
             const int tile = t_begin + st;
             if (tile < t_end && (tile + 1) * FA_BN <= new_from)
-                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
+                loader.load(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, tile * FA_BN);
             cp_async_commit();
         }
         // (asking for the tiles beyond those into L2 was measured: no gain at batch 8, a loss at 64)
@@ -254,7 +291,7 @@ attention_fa_kernel(const FaParams p) {
         for (int st = 0; st < NST - 1; ++st) {
             const int tile = t_begin + st;
             if (tile < t_end && (tile + 1) * FA_BN > new_from)
-                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, tile * FA_BN, kv_len);
+                loader.load(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, tile * FA_BN);
         }
         cp_async_commit();
     } else {
@@ -262,7 +299,7 @@ attention_fa_kernel(const FaParams p) {
 #pragma unroll
         for (int st = 0; st < NST - 1; ++st) {
             if (t_begin + st < t_end)
-                load_kv_tile<HD>(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, p.pool, p.kv, slot, kvh, (t_begin + st) * FA_BN, kv_len);
+                loader.load(k_sm + st * TILE_BYTES, v_sm + st * TILE_BYTES, (t_begin + st) * FA_BN);
             cp_async_commit();
         }
     }
@@ -298,7 +335,7 @@ attention_fa_kernel(const FaParams p) {
             // the tile NST - 1 ahead goes into the buffer that the previous iteration finished with
             const int ahead = tile + NST - 1, abuf = (ahead - t_begin) % NST;
             if (ahead < t_end)
-                load_kv_tile<HD>(k_sm + abuf * TILE_BYTES, v_sm + abuf * TILE_BYTES, p.pool, p.kv, slot, kvh, ahead * FA_BN, kv_len);
+                loader.load(k_sm + abuf * TILE_BYTES, v_sm + abuf * TILE_BYTES, ahead * FA_BN);
             cp_async_commit();
         }
         if (DECODE && tile == t_begin) cp_async_wait_all();   // queries included
