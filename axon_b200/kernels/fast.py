@@ -21,7 +21,8 @@ SMALL_M = 64
 
 #: switches for tests that compare a tuned kernel with the plain one
 ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attention_prefill": True,
-           "attention_decode": True, "attention_tc": True, "attention_fused": True}
+           "attention_decode": True, "attention_tc": True,
+           "attention_fused": os.environ.get("AXON_FA_FUSED", "1") != "0"}
 
 
 def _stream() -> int:
@@ -170,8 +171,10 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
 
 FA_HEAD_DIMS = (16, 32, 64, 128)
 FA_MAX_SPLITS = 32
-#: CTAs the decode attention aims at when it splits the keys of each request
-FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 2 * 148))
+#: CTAs the decode attention aims at (and does not exceed) when it splits the keys of each request:
+#: two CTAs fit an SM, and a launch that spills into a second wave pays for it (measured at 7B
+#: sizes: 320 CTAs at batch 16 cost 10 % of the step against 256)
+FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 256))
 #: whether the last split folds the partials itself (else a second kernel does; measured at 7B
 #: sizes the second kernel is a little faster up to batch 8 and equal at 64, because it overlaps
 #: with the kernels around it while the in-kernel fold lengthens the slowest CTA)
@@ -224,10 +227,8 @@ def _attention_items(ctx, group: int, pre_rows: int = 64):
 
 def _decode_splits(n_dec: int, kv, tiles: int, rt):
     """Key splits for the decode shape and the scratch their partials go to (None: a cluster folds)."""
-    # small batches: about two CTAs per SM; large ones (a CTA per request and kv head fills
-    # the machine already) still gain from three or four shares of the keys
-    target = FA_TARGET_CTAS if n_dec * kv.kv_heads < SM_COUNT else 2 * FA_TARGET_CTAS
-    splits = max(1, min(tiles, FA_MAX_SPLITS, -(-target // (n_dec * kv.kv_heads))))
+    target = FA_TARGET_CTAS
+    splits = max(1, min(tiles, FA_MAX_SPLITS, target // (n_dec * kv.kv_heads)))
     scratch = None
     # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
     # no second kernel); longer contexts keep more, independent splits
@@ -236,7 +237,7 @@ def _decode_splits(n_dec: int, kv, tiles: int, rt):
     elif splits > 1:
         # sized for the most splits this batch can get, so that the buffer never moves
         # while the contexts grow (captured graphs hold its address)
-        most = min(FA_MAX_SPLITS, -(-target // (n_dec * kv.kv_heads)))
+        most = max(1, min(FA_MAX_SPLITS, target // (n_dec * kv.kv_heads)))
         scratch = rt.buffer("fa_scratch", (n_dec * kv.kv_heads * most * 16 * (kv.head_dim + 2),), torch.float32)
     return splits, scratch
 
