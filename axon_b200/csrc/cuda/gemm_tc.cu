@@ -347,7 +347,7 @@ __device__ __forceinline__ void swap_store(float v, float old, int row, int tok,
 template <int NTOK, int STAGES, int EPI, int R>
 __global__ void __launch_bounds__(192)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const float* __restrict__ bias, void* __restrict__ out, float* __restrict__ partial,
+                    const float* __restrict__ bias, void* out, float* __restrict__ partial,
                     unsigned int* __restrict__ counters, int M, int N, int K, int ldo, int splits, int per_split) {
     constexpr uint32_t W_BYTES = R * 128 * TC_BK * 2, X_BYTES = NTOK * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr uint32_t TMEM_COLS = R * NTOK < 32 ? 32 : R * NTOK;
@@ -362,6 +362,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / splits, split = blockIdx.x % splits;
     const int n0 = tile * 128 * R;
+    // more than NTOK tokens: blockIdx.y picks the block of NTOK; M_all tokens in all, Mb in this block
+    const int t0 = blockIdx.y * NTOK, M_all = M, m_pad = gridDim.y * NTOK;
+    M = min(NTOK, M_all - t0);
+    out = EPI == TC_STORE_BF16 || EPI == TC_SWIGLU ? (void*)((__nv_bfloat16*)out + (long long)t0 * ldo)
+                                                   : (void*)((float*)out + (long long)t0 * ldo);
     const int k_total = (K + TC_BK - 1) / TC_BK;
     const int ks_begin = split * per_split, ks_end = min(k_total, ks_begin + per_split);
     const int k_stages = ks_end - ks_begin;          // >= 1 by construction of `splits`
@@ -397,14 +402,14 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // boxes the more, because the requests queue ahead of the loads that follow)
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
-                tma_load_2d(smem_base + i * STAGE_BYTES + W_BYTES, &map_x, (ks_begin + i) * TC_BK, 0, full0 + 8 * i);
+                tma_load_2d(smem_base + i * STAGE_BYTES + W_BYTES, &map_x, (ks_begin + i) * TC_BK, t0, full0 + 8 * i);
             for (int i = ahead; i < k_stages; ++i) {
                 const int s = i % STAGES;
                 mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, 0);
                 const uint32_t sw = smem_base + s * STAGE_BYTES, sx = sw + W_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(sw, &map_w, (ks_begin + i) * TC_BK, n0, full0 + 8 * s);
-                tma_load_2d(sx, &map_x, (ks_begin + i) * TC_BK, 0, full0 + 8 * s);
+                tma_load_2d(sx, &map_x, (ks_begin + i) * TC_BK, t0, full0 + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -452,36 +457,41 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc_fence_before();
         } else {
         const int row = n0 + quarter * 32 + lane;                  // this lane's weight row
-        float acc[NTOK];
-#pragma unroll
-        for (int c = 0; c < NTOK / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(lane_addr + (uint32_t)(c * 16), r);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = __uint_as_float(r[i]);
-        }
-        tc_fence_before();
         if (splits == 1) {
-            float old[NTOK];
+            // sixteen tokens at a time: tensor memory -> epilogue -> memory
+#pragma unroll 1
+            for (int c = 0; c < NTOK / 16 && c * 16 < M; ++c) {
+                uint32_t r[16];
+                float old[16];
+                tmem_ld16(lane_addr + (uint32_t)(c * 16), r);
 #pragma unroll
-            for (int j = 0; j < NTOK; ++j) old[j] = (j < M) ? swap_old<EPI>(row, j, N, out, ldo) : 0.f;
+                for (int i = 0; i < 16; ++i) old[i] = (c * 16 + i < M) ? swap_old<EPI>(row, c * 16 + i, N, out, ldo) : 0.f;
 #pragma unroll
-            for (int j = 0; j < NTOK; ++j)
-                if (j < M) swap_store<EPI>(acc[j], old[j], row, j, N, bias, out, ldo);
+                for (int i = 0; i < 16; ++i)
+                    if (c * 16 + i < M) swap_store<EPI>(__uint_as_float(r[i]), old[i], row, c * 16 + i, N, bias, out, ldo);
+            }
+            tc_fence_before();
         } else {
-            // partial[split][token][row of this tile]; then the last CTA of the tile folds
-            float* mine = partial + ((long long)(tile * splits + split) * NTOK) * 128 + quarter * 32 + lane;
+            // partial[tile][split][token][row of this tile]; then the last CTA of the tile folds
+            // (or, without counters, the reader of the output does)
+            float* mine = partial + ((long long)(tile * splits + split) * m_pad + t0) * 128 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < NTOK / 16 && c * 16 < M; ++c) {
+                uint32_t r[16];
+                tmem_ld16(lane_addr + (uint32_t)(c * 16), r);
 #pragma unroll
-            for (int j = 0; j < NTOK; ++j)
-                if (j < M) mine[j * 128] = acc[j];
+                for (int i = 0; i < 16; ++i)
+                    if (c * 16 + i < M) mine[(c * 16 + i) * 128] = __uint_as_float(r[i]);
+            }
+            tc_fence_before();
             if (counters != nullptr) {
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps
-            if (threadIdx.x == 64) arrival = atomicAdd(&counters[tile], 1u);
+            if (threadIdx.x == 64) arrival = atomicAdd(&counters[tile * gridDim.y + blockIdx.y], 1u);
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (arrival == (unsigned)(splits - 1)) {
                 __threadfence();
-                const float* all = partial + ((long long)tile * splits * NTOK) * 128 + quarter * 32 + lane;
+                const float* all = partial + ((long long)tile * splits * m_pad + t0) * 128 + quarter * 32 + lane;
                 // G tokens and four slabs at a time: up to 64 independent loads in flight per
                 // thread, summed in slab order (adding the zeros of absent slabs changes nothing)
                 constexpr int G = NTOK >= 32 ? 16 : 8;
@@ -501,7 +511,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                             for (int q = 0; q < 4; ++q)
                                 t[u][q] = (j0 + u < M && s0 + q < splits)
-                                              ? __ldcg(all + ((long long)(s0 + q) * NTOK + j0 + u) * 128) : 0.f;
+                                              ? __ldcg(all + ((long long)(s0 + q) * m_pad + j0 + u) * 128) : 0.f;
 #pragma unroll
                         for (int u = 0; u < G; ++u)
 #pragma unroll
@@ -511,7 +521,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     for (int u = 0; u < G; ++u)
                         if (j0 + u < M) swap_store<EPI>(v[u], old[u], row, j0 + u, N, bias, out, ldo);
                 }
-                if (threadIdx.x == 64) counters[tile] = 0u;               // ready for the next launch
+                if (threadIdx.x == 64) counters[tile * gridDim.y + blockIdx.y] = 0u;   // ready for the next launch
             }
             }   // counters: this kernel folds
         }
@@ -703,7 +713,8 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
                        float* partial, unsigned int* counters, int M, int N, int K, int ldo, int tiles, int splits,
                        int per_split, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * (R * 128 * TC_BK * 2 + NTOK * TC_BK * 2) + 1024;
-    const dim3 grid((unsigned)(tiles * splits)), block(192);
+    static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
+    const dim3 grid((unsigned)(tiles * splits), (unsigned)((M + NTOK - 1) / NTOK)), block(192);
 #define AXON_SWAP_LAUNCH(E)                                                                                        \
     {                                                                                                              \
         static bool configured = false;                                                                            \
@@ -726,7 +737,9 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
 }
 }  // namespace axon
 
-// The product for at most 64 activation rows (see gemm_tc_swap_kernel).  `partial` is
+// The product for at most 1024 activation rows (see gemm_tc_swap_kernel): the weights are read
+// once per block of 256 tokens, which beats the 256 x 256 tiles of axon_gemm_tc while the
+// product is bound by reading weights and its tiles would not fill the machine.  `partial` is
 // scratch for split-K partial tiles (`partial_floats` floats; 0 forbids splitting) and
 // `counters` an array of `n_counters` zeroed 32-bit counters that the kernel leaves zeroed.
 // `target_ctas` is the number of CTAs to aim at (the SM count works best: one CTA per SM
@@ -736,17 +749,19 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
 // sums in `partial` for the reader of the output (SplitFold: axon_rmsnorm_fold,
 // axon_rope_kv_write, axon_fold_partials), which must run before `partial` is written again;
 // bias and residual are then the reader's to add and `out` is not touched.
-// `plan` (may be null) receives {splits, token columns of the partial tiles, deferred 0/1}.
+// `plan` (may be null) receives {splits, token rows of the partial tiles (M padded), deferred 0/1}.
 AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias, void* out, int epilogue, int M,
                                 int N, int K, int ldo, float* partial, long long partial_floats,
                                 unsigned int* counters, int n_counters, int target_ctas, int defer, int* plan,
                                 cudaStream_t stream) {
     if (M <= 0 || N <= 0) return AXON_OK;
-    if (M > 64) { set_error("axon_gemm_tc_small: %d rows; this kernel takes at most 64", M); return AXON_BAD_ARGUMENT; }
+    if (M > 1024) { set_error("axon_gemm_tc_small: %d rows; this kernel takes at most 1024", M); return AXON_BAD_ARGUMENT; }
     if (K <= 0 || K % 8) { set_error("axon_gemm_tc_small: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc_small: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc_small: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
-    const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    // tokens are the MMA's columns: padded to 16 .. 256, and in blocks of 256 beyond that
+    const int ntok = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const int blocks = (M + ntok - 1) / ntok, m_pad = blocks * ntok;
     const int tiles128 = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
     // many rows: 256-row tiles halve the CTA count (no split then)
     // (measured at 7B sizes: with 2 x target tiles, two 128-row CTAs per SM and six stages beat
@@ -755,24 +770,26 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     const int tiles = wide ? (N + 255) / 256 : tiles128;
     // few rows: as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
     int splits = 1;
-    if (!wide && partial != nullptr && counters != nullptr && tiles <= n_counters && tiles < target_ctas) {
-        splits = (target_ctas + tiles / 2) / tiles;
+    if (!wide && partial != nullptr && counters != nullptr && tiles * blocks <= n_counters && tiles * blocks < target_ctas) {
+        splits = (target_ctas + tiles * blocks / 2) / (tiles * blocks);
         if (splits > k_total / 4) splits = k_total / 4;
-        const long long fit = partial_floats / ((long long)tiles * ntok * 128);
+        const long long fit = partial_floats / ((long long)tiles * m_pad * 128);
         if (splits > fit) splits = (int)fit;
         if (splits < 1) splits = 1;
     }
     const int per_split = (k_total + splits - 1) / splits;
     splits = (k_total + per_split - 1) / per_split;
     const bool deferred = defer && splits > 1 && (epilogue == TC_STORE_F32 || epilogue == TC_RESIDUAL);
-    if (plan) { plan[0] = splits; plan[1] = ntok; plan[2] = deferred ? 1 : 0; }
+    if (plan) { plan[0] = splits; plan[1] = m_pad; plan[2] = deferred ? 1 : 0; }
     if (deferred) counters = nullptr;                 // the kernel stops after writing its partial tile
     CUtensorMap mw, mx;
     if (!tensor_map(w, N, K, wide ? 256 : 128, &mw) || !tensor_map(a, M, K, ntok, &mx)) return AXON_BAD_ARGUMENT;
 #define AXON_SWAP_ARGS epilogue, mw, mx, bias, out, partial, counters, M, N, K, ldo, tiles, splits, per_split, stream
     if (ntok == 16) return wide ? launch_swap<16, 3, 2>(AXON_SWAP_ARGS) : launch_swap<16, 6, 1>(AXON_SWAP_ARGS);
     if (ntok == 32) return wide ? launch_swap<32, 3, 2>(AXON_SWAP_ARGS) : launch_swap<32, 5, 1>(AXON_SWAP_ARGS);
-    return launch_swap<64, 4, 1>(AXON_SWAP_ARGS);
+    if (ntok == 64) return launch_swap<64, 4, 1>(AXON_SWAP_ARGS);
+    if (ntok == 128) return launch_swap<128, 5, 1>(AXON_SWAP_ARGS);
+    return launch_swap<256, 4, 1>(AXON_SWAP_ARGS);
 #undef AXON_SWAP_ARGS
 }
 

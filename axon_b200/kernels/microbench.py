@@ -107,7 +107,9 @@ def main() -> int:
         else:
             out = torch.zeros(a.m, a.n, dtype=torch.bfloat16 if a.epilogue == "bf16" else torch.float32, device=DEV)
             fn = lambda: fast.gemm(x, w, out, None, a.epilogue == "residual")
-        if a.kernel == "gemm_tc" and a.m <= fast.SMALL_M:
+        if a.kernel == "gemm_small_m":
+            fast.SMALL_M = fast.SWAP_MAX_ROWS = 1024                               # the swapped kernel at any size it takes
+        if a.kernel == "gemm_tc":
             fast.ENABLED["gemm_small_m"] = fast.ENABLED["gemm_tc_small"] = False   # the 128-row-tile kernel
         if a.tile:
             rm, bn = a.tile.split("x")

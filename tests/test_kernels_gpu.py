@@ -381,9 +381,10 @@ def tile_shape(request):
 
 @pytest.mark.parametrize("M", [65, 129, 300, 1100])
 @pytest.mark.parametrize("N,K", [(256, 64), (128, 8), (130, 72), (1000, 160), (344, 344), (2, 1096), (4608, 3584)])
-def test_gemm_tensor_core(ops, tile_shape, M, N, K):
+def test_gemm_tensor_core(ops, tile_shape, M, N, K, monkeypatch):
     """The tcgen05 kernel at sizes with tails in M, N and K, every epilogue, every tile shape."""
     from axon_b200.kernels import fast
+    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 64)          # the tiled kernel, also where the swapped one would run
     a = rand(M, K, dtype=torch.bfloat16, seed=80)
     w = rand(N, K, dtype=torch.bfloat16, seed=81, std=0.1)
     bias = rand(N, seed=82)
@@ -413,11 +414,48 @@ def test_gemm_tensor_core(ops, tile_shape, M, N, K):
     assert fast.gemm_tc_status() == 0, "a wait inside the kernel gave up"
 
 
+@pytest.mark.parametrize("M", [65, 128, 129, 256, 300, 700, 1024])
+@pytest.mark.parametrize("N,K", [(256, 64), (130, 72), (1000, 160), (3584, 1024), (2, 1096)])
+def test_gemm_swapped_in_blocks_of_tokens(ops, M, N, K, monkeypatch):
+    """The product with the tokens as the MMA's columns beyond 64 rows: 128 or 256 columns, and
+    blocks of 256 tokens beyond that; every epilogue, split over K or not, folded by itself or by the reader."""
+    from axon_b200.kernels import fast
+    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 1024)
+    monkeypatch.setattr(fast, "_takes_swapped_kernel", lambda m, n: True)
+    a = rand(M, K, dtype=torch.bfloat16, seed=140)
+    w = rand(N, K, dtype=torch.bfloat16, seed=141, std=0.1)
+    bias = rand(N, seed=142)
+    res = rand(M, N, seed=143)
+    want = a.double() @ w.double().T
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    assert fast.gemm(a, w, out, bias, False) is True
+    close(out, want + bias.double(), 2e-5, "float output")
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert fast.gemm(a, w, outb, None, False) is True
+    close(outb, want, OUT_TOL[torch.bfloat16], "bfloat16 output")
+    acc = res.clone()
+    assert fast.gemm(a, w, acc, None, True) is True
+    close(acc, want + res.double(), 2e-5, "into the residual")
+    acc2 = res.clone()
+    owed = fast.gemm(a, w, acc2, None, True, defer=True)
+    if isinstance(owed, fast.PendingFold):
+        assert owed.ntok >= M and owed.ntok % 16 == 0
+        ops.fold_partials(owed)
+    assert torch.equal(acc2, acc), "the reader's fold differs from the kernel's"
+    if N % 2 == 0:
+        act = torch.full((M, N // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+        assert fast.gemm_swiglu(a, w, act)
+        g, u = want[:, 0::2], want[:, 1::2]
+        close(act, g / (1 + torch.exp(-g)) * u, OUT_TOL[torch.bfloat16], "SwiGLU epilogue")
+    assert fast.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(300, 1024, 160), (1100, 4608, 512)])
-def test_gemm_tensor_core_output_paths(ops, M, N, K):
+def test_gemm_tensor_core_output_paths(ops, M, N, K, monkeypatch):
     """Outputs that TMA can address leave through shared memory and TMA (clipped at the edges, the
     residual by TMA's add); the others are stored from registers.  Both give the same numbers."""
     from axon_b200.kernels import fast, lib
+    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 64)
     a = rand(M, K, dtype=torch.bfloat16, seed=90)
     w = rand(N, K, dtype=torch.bfloat16, seed=91, std=0.1)
     bias = rand(N, seed=92)
