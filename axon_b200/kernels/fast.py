@@ -36,8 +36,7 @@ ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attent
            "attention_fused": os.environ.get("AXON_FA_FUSED", "1") != "0"}
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+_stream = lib.current_stream
 
 
 _SPLIT_SCRATCH = {}

@@ -162,3 +162,14 @@ def check(status: int) -> None:
     if status != 0:
         msg = cuda().axon_last_error().decode("utf-8", "replace")
         raise KernelError(msg or f"kernel launcher returned {status}")
+
+
+def current_stream() -> int:
+    """The raw handle of PyTorch's current CUDA stream on the current device.  Asked for at
+    every launch, so it goes through the one C call PyTorch has for it when that exists
+    (``torch.cuda.current_stream()`` costs several microseconds of Python)."""
+    import torch
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return raw(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
