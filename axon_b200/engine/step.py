@@ -56,6 +56,11 @@ class Engine:
         #: rows and attention split count), as the reference captures its decode step
         #: (src/cuda/qwen2.rs:2978-3011; per step shape: src/cuda/qwen2/slots.rs:722-785)
         self.cuda_graphs = bool(model.graph_safe)
+        #: a prompt portion of one request whose size comes a second time is captured too (chunked
+        #: prefill repeats its chunk size): the host's share of such a step, about 12 us a launch,
+        #: is what bounds prompts of a few hundred tokens
+        self.prefill_graphs = bool(model.graph_safe)
+        self._shape_seen = {}
         self.graph_max_batch = 256
         self.graph_cache_size = 64
         self._graphs = {}
@@ -206,7 +211,17 @@ class Engine:
         graph_key = None
         if self.cuda_graphs and decode_only and n <= self.graph_max_batch:
             graph_key = (n, n_want, min(32, -(-max(seg_kv_len) // 64)), bool(greedy))
-        meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{graph_key[0]}_{graph_key[1]}"
+        elif self.cuda_graphs and self.prefill_graphs and s == 1 and n > 1:
+            # one request's portion: nothing the host works out for it depends on where in the
+            # request it lies (positions, lengths and tables are read from device memory)
+            key = ("portion", n, n_want, bool(greedy))
+            seen = self._shape_seen.get(key, 0) + 1
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            self._shape_seen[key] = seen
+            if seen >= 2:
+                graph_key = key
+        meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{graph_key[0]}_{graph_key[1]}_{graph_key[2]}"
         dev = self.rt.buffer(meta_name, (total,), torch.int32)
         dev.copy_(stage[:total], non_blocking=True)
         ev = torch.cuda.Event()
@@ -277,8 +292,11 @@ class Engine:
                         self._graphs.pop(next(iter(self._graphs)))
                     self._graphs[key] = (graph, launches)
             except RuntimeError:
-                # capture failed (for instance a part that allocates): steps of this shape stay eager
-                self.cuda_graphs = False
+                # capture failed (for instance a part that allocates): steps of this kind stay eager
+                if key[0] == "portion":
+                    self.prefill_graphs = False
+                else:
+                    self.cuda_graphs = False
         else:
             self._graph_generation = self.rt.generation
         return result

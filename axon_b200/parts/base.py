@@ -47,6 +47,8 @@ class Runtime:
         self.precise = dtype == torch.float32
         self._buffers: Dict[str, torch.Tensor] = {}
         self._pinned: Dict[str, Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = {}
+        self._uploads: Dict[Any, torch.Tensor] = {}
+        self._uploads_held = set()
         #: raised whenever an existing scratch buffer is replaced by a larger one: addresses
         #: handed out before are stale from then on (captured CUDA graphs must be dropped)
         self.generation = 0
@@ -65,10 +67,22 @@ class Runtime:
         return buf[:n].view(shape)
 
     def upload_i32(self, name: str, values) -> torch.Tensor:
-        """Host integers to a named device buffer through pinned memory, without blocking the
-        host (a tensor made from a Python list goes through pageable memory and stalls the
-        stream).  The pinned copy of a name is reused once its last transfer has finished."""
+        """Host integers (a work list, say) as a device tensor.  The same list under the same name
+        is uploaded once and kept, so steps of a shape seen before copy nothing, and a CUDA graph
+        may hold the tensor's address (lists first met inside a capture are refused: the capture
+        fails and the step stays eager).  New lists go through pinned memory without blocking."""
         import numpy as np
+        key = (name, tuple(values))
+        capturing = torch.cuda.is_current_stream_capturing()
+        hit = self._uploads.get(key)
+        if hit is not None:
+            if capturing:
+                self._uploads_held.add(key)          # a graph reads it from now on: never dropped
+            else:
+                self._uploads[key] = self._uploads.pop(key)      # most recently used last
+            return hit
+        if capturing:
+            raise RuntimeError("a host list would be uploaded for the first time inside a graph capture")
         n = len(values)
         host, event = self._pinned.get(name, (None, None))
         if event is not None:
@@ -76,11 +90,18 @@ class Runtime:
         if host is None or host.numel() < n:
             host = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
         host.numpy()[:n] = np.asarray(values, dtype=np.int32)
-        dev = self.buffer(name, (n,), torch.int32)
+        dev = torch.empty(max(n, 1), dtype=torch.int32, device=self.device)[:n]
         dev.copy_(host[:n], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._pinned[name] = (host, event)
+        self._uploads[key] = dev
+        if len(self._uploads) > 256:
+            for old in list(self._uploads):
+                if len(self._uploads) <= 192:
+                    break
+                if old not in self._uploads_held and old != key:
+                    del self._uploads[old]
         return dev
 
     def release_buffers(self) -> None:
