@@ -15,6 +15,8 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 namespace axon {
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -29,9 +31,11 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
+    // AXON_PDL=0 in the environment launches everything fully serialised (for measurements)
+    static const int allowed = [] { const char* e = getenv("AXON_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = allowed;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
