@@ -60,6 +60,13 @@ class DecoderModel:
         e = self.spec.schedule[entry]
         return entry if e.cache_of is None else e.cache_of
 
+    def graph_key(self, ctx: StepContext):
+        """The parts' host-side launch parameters for this step (see ``Part.graph_key``), once each."""
+        keys = set()
+        for part in [self.embedding, self.final_norm, self.head, *self.blocks]:
+            keys.update(part.graph_key(ctx))
+        return tuple(sorted(keys, key=repr))
+
     def forward(self, ctx: StepContext, cache: Any, want_rows: Optional[torch.Tensor], n_want: int,
                 logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the step's tokens through every schedule entry; the float32 logits of

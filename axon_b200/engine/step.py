@@ -210,7 +210,11 @@ class Engine:
         # (tokens, positions, slots, lengths, block tables) is read from device memory.
         graph_key = None
         if self.cuda_graphs and decode_only and n <= self.graph_max_batch:
-            graph_key = (n, n_want, min(32, -(-max(seg_kv_len) // 64)), bool(greedy))
+            # what the parts' launches take from the host beside the batch shape (the attention's
+            # split count follows the longest context) is part of the key
+            probe = StepContext(rt=self.rt, n_tokens=n, tokens=None, positions=None, token_slot=None,
+                                seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len)
+            graph_key = (n, n_want, self.model.graph_key(probe), bool(greedy))
         elif self.cuda_graphs and self.prefill_graphs and s == 1 and n > 1:
             # one request's portion: nothing the host works out for it depends on where in the
             # request it lies (positions, lengths and tables are read from device memory)
@@ -221,7 +225,7 @@ class Engine:
             self._shape_seen[key] = seen
             if seen >= 2:
                 graph_key = key
-        meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{graph_key[0]}_{graph_key[1]}_{graph_key[2]}"
+        meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{'p' if graph_key[0] == 'portion' else 'd'}_{n}_{n_want}"
         dev = self.rt.buffer(meta_name, (total,), torch.int32)
         dev.copy_(stage[:total], non_blocking=True)
         ev = torch.cuda.Event()

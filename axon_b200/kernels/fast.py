@@ -235,6 +235,13 @@ def _attention_items(ctx, group: int, pre_rows: int = 64):
     return got
 
 
+def decode_split_count(n_dec: int, kv_heads: int, max_kv_len: int) -> int:
+    """Into how many shares the decode attention cuts each request's keys: the one launch
+    parameter of a step of single tokens that depends on the contexts' lengths."""
+    tiles = -(-max_kv_len // 64)
+    return max(1, min(tiles, FA_MAX_SPLITS, FA_TARGET_CTAS // (n_dec * kv_heads)))
+
+
 def _decode_splits(n_dec: int, kv, tiles: int, rt):
     """Key splits for the decode shape and the scratch their partials go to (None: a cluster folds)."""
     target = FA_TARGET_CTAS

@@ -170,6 +170,12 @@ class Part:
     def tensors(cls, spec: PartSpec) -> Dict[str, TensorDecl]:
         return {}
 
+    def graph_key(self, ctx: "StepContext") -> Tuple:
+        """Whatever this part's launches take from the host that differs between two steps of
+        the same batch shape (a split count that follows the context length, say).  Steps of
+        single tokens replay a captured CUDA graph when batch shape and these keys agree."""
+        return ()
+
     @classmethod
     def cache_need(cls, spec: PartSpec) -> Union[KvNeed, StateNeed, None]:
         return None

@@ -146,6 +146,12 @@ class Attention(Mixer):
         self.b_o = tensors.get("o_bias") if p.get("out_bias") else None
         self.position = build(spec.parts["position"]) if "position" in spec.parts else None
 
+    def graph_key(self, ctx: StepContext):
+        if self.rt.precise:
+            return ()
+        from ..kernels import fast
+        return (("key_splits", fast.decode_split_count(len(ctx.seg_slot), self.kv_heads, ctx.max_kv_len)),)
+
     def forward(self, h, x, ctx: StepContext, cache: ops.KvView, write_cache: bool = True, defer: bool = False):
         rt, n = self.rt, ctx.n_tokens
         qkv = rt.buffer("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
@@ -213,6 +219,9 @@ class PreNormBlock(Part):
         self.mixer = build(spec.parts["mixer"])
         self.norm_ffn = build(spec.parts["norm_ffn"])
         self.ffn = build(spec.parts["ffn"])
+
+    def graph_key(self, ctx: StepContext):
+        return self.norm_mixer.graph_key(ctx) + self.mixer.graph_key(ctx) + self.norm_ffn.graph_key(ctx) + self.ffn.graph_key(ctx)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, write_cache: bool = True, pending=None):
         """``pending``: what ``x`` is still owed on entry; returns what it is owed on exit."""
