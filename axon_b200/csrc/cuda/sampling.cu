@@ -39,6 +39,64 @@ __device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v
     return v;
 }
 
+// f(value, index) for every element of a row, each thread taking every blockDim-th float4 with
+// eight loads in flight (rows that are not 16-byte aligned go element by element).
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F f) {
+    int tail = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const int n4 = vocab >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 8 * blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < n4 ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i < n4) { f(v[u].x, 4 * i); f(v[u].y, 4 * i + 1); f(v[u].z, 4 * i + 2); f(v[u].w, 4 * i + 3); }
+            }
+        }
+        tail = n4 << 2;
+    }
+    for (int i = tail + threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+}
+
+// hist[256] counts a digit; `rem` of the largest are still wanted.  Returns the digit in which
+// the rem-th largest lies and takes the counts of the digits above it off `rem`.  One warp.
+__device__ __forceinline__ int digit_of_rank(const unsigned int* hist, int& rem) {
+    const int lane = threadIdx.x & 31;
+    // lane l owns digits 255 - 8 l .. 248 - 8 l, from the top
+    unsigned int mine[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { mine[j] = hist[255 - 8 * lane - j]; sum += mine[j]; }
+    unsigned int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const unsigned int before = incl - sum;                       // count in the digits above this lane's
+    const unsigned int hit = __ballot_sync(0xffffffffu, incl >= (unsigned)rem);
+    const int owner = hit ? __ffs(hit) - 1 : 31;
+    int d = 0, r = rem;
+    if (lane == owner) {
+        r = rem - (int)before;
+        int j = 0;
+        for (; j < 7; ++j) {
+            if ((int)mine[j] >= r) break;
+            r -= (int)mine[j];
+        }
+        d = 255 - 8 * lane - j;
+    }
+    d = __shfl_sync(0xffffffffu, d, owner);
+    rem = __shfl_sync(0xffffffffu, r, owner);
+    return d;
+}
+
 // best[r] = the id of the largest logit of row r (last index among equal maxima;
 // a NaN is picked only when the whole row is NaN, then the last index).
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ best, int vocab,
@@ -103,55 +161,119 @@ __global__ void penalty_kernel(float* __restrict__ logits, const int32_t* __rest
 // 64-bit key (logit key, id): keys are distinct, so exactly k pass the threshold.
 constexpr int CAND_MAX = 256;
 
+constexpr int TOPK_POOL = 4096;      // candidates of the deciding top byte that fit shared memory
+
+// General form: eight passes over the whole row, one per byte of the key.  For rows whose
+// deciding top byte holds more values than the pool (thousands of nearly equal logits).
+__device__ void topk_select_general(const float* __restrict__ row, int vocab, int k, unsigned int* hist,
+                                    unsigned long long* picked, int* n_picked, unsigned long long* prefix_s, int* remaining_s) {
+    if (threadIdx.x == 0) { *prefix_s = 0ull; *remaining_s = k; *n_picked = 0; }
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+        __syncthreads();
+        const unsigned long long prefix = *prefix_s;
+        for_each_logit(row, vocab, [&](float v, int i) {
+            const unsigned long long key = key64(v, i);
+            if (shift == 56 || (key >> (shift + 8)) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+        });
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int rem = *remaining_s;
+            const int d = digit_of_rank(hist, rem);
+            if (threadIdx.x == 0) { *prefix_s = (prefix << 8) | (unsigned)d; *remaining_s = rem; }
+        }
+        __syncthreads();
+    }
+    const unsigned long long kth = *prefix_s;  // the k-th largest key
+    for_each_logit(row, vocab, [&](float v, int i) {
+        const unsigned long long key = key64(v, i);
+        if (key >= kth) {
+            const int at = atomicAdd(n_picked, 1);
+            if (at < CAND_MAX) picked[at] = key;
+        }
+    });
+    __syncthreads();
+}
+
+// Two passes over the row: a histogram of the key's top byte (a counter array per warp, so that
+// the many values of one byte do not queue on one counter) finds the byte in which the k-th
+// largest lies; the second pass takes everything above that byte and pools the values of that
+// byte in shared memory, where seven more passes over the few pooled keys settle the rest.
 __global__ void __launch_bounds__(1024)
 topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
             float* __restrict__ cand_logit, int32_t* __restrict__ cand_id, int vocab,
             long long row_stride) {
+    extern __shared__ __align__(16) unsigned char topk_smem[];   // 32 KiB: per-warp histograms, then the pool
+    unsigned int* warp_hist = reinterpret_cast<unsigned int*>(topk_smem);            // [32][256]
+    unsigned long long* pool = reinterpret_cast<unsigned long long*>(topk_smem);       // [TOPK_POOL]
     __shared__ unsigned int hist[256];
     __shared__ unsigned long long prefix_s;
-    __shared__ int remaining_s;
+    __shared__ int remaining_s, n_picked, n_pool;
     __shared__ unsigned long long picked[CAND_MAX];
-    __shared__ int n_picked;
-    const int r = blockIdx.x;
+    const int r = blockIdx.x, warp = threadIdx.x >> 5;
     const float* row = logits + (long long)r * row_stride;
     int k = ks[r];
     if (k > vocab) k = vocab;
     if (k > CAND_MAX) k = CAND_MAX;
     if (k <= 0) return;
 
-    if (threadIdx.x == 0) { prefix_s = 0ull; remaining_s = k; n_picked = 0; }
-    // digits of the key from the top: 4 bytes of logit key, then 4 bytes of id
-    for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
-        __syncthreads();
-        const unsigned long long prefix = prefix_s;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const unsigned long long key = key64(row[i], i);
-            if (shift == 56 || (key >> (shift + 8)) == prefix)
-                atomicAdd(&hist[(key >> shift) & 0xff], 1u);
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int rem = remaining_s;
-            int d = 255;
-            for (; d > 0; --d) {
-                if ((int)hist[d] >= rem) break;
-                rem -= (int)hist[d];
-            }
-            prefix_s = (prefix << 8) | (unsigned)d;
-            remaining_s = rem;
-        }
-        __syncthreads();
-    }
-    const unsigned long long kth = prefix_s;  // the k-th largest key
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const unsigned long long key = key64(row[i], i);
-        if (key >= kth) {
-            const int at = atomicAdd(&n_picked, 1);
-            if (at < CAND_MAX) picked[at] = key;
-        }
+    for (int i = threadIdx.x; i < 32 * 256; i += blockDim.x) warp_hist[i] = 0u;
+    if (threadIdx.x == 0) { n_picked = 0; n_pool = 0; }
+    __syncthreads();
+    for_each_logit(row, vocab, [&](float v, int) { atomicAdd(&warp_hist[warp * 256 + (logit_key(v) >> 24)], 1u); });
+    __syncthreads();
+    for (int d = threadIdx.x; d < 256; d += blockDim.x) {
+        unsigned int c = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; ++w) c += warp_hist[w * 256 + d];
+        hist[d] = c;
     }
     __syncthreads();
+    if (threadIdx.x < 32) {
+        int rem = k;
+        const int d = digit_of_rank(hist, rem);
+        if (threadIdx.x == 0) { prefix_s = (unsigned long long)d; remaining_s = rem; }
+    }
+    __syncthreads();
+    const unsigned int top = (unsigned int)prefix_s;
+    const bool fits = hist[top] <= (unsigned)TOPK_POOL;
+    if (fits) {
+        for_each_logit(row, vocab, [&](float v, int i) {
+            const unsigned int d = logit_key(v) >> 24;
+            if (d > top) picked[atomicAdd(&n_picked, 1)] = key64(v, i);          // fewer than k of them
+            else if (d == top) pool[atomicAdd(&n_pool, 1)] = key64(v, i);
+        });
+        __syncthreads();
+        // the remaining seven bytes, over the pool only
+        const int n = n_pool;
+        for (int shift = 48; shift >= 0; shift -= 8) {
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
+            __syncthreads();
+            const unsigned long long prefix = prefix_s;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const unsigned long long key = pool[i];
+                if ((key >> (shift + 8)) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+            }
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                int rem = remaining_s;
+                const int d = digit_of_rank(hist, rem);
+                if (threadIdx.x == 0) { prefix_s = (prefix << 8) | (unsigned)d; remaining_s = rem; }
+            }
+            __syncthreads();
+        }
+        const unsigned long long kth = prefix_s;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const unsigned long long key = pool[i];
+            if (key >= kth) {
+                const int at = atomicAdd(&n_picked, 1);
+                if (at < CAND_MAX) picked[at] = key;
+            }
+        }
+        __syncthreads();
+    } else {
+        topk_select_general(row, vocab, k, hist, picked, &n_picked, &prefix_s, &remaining_s);
+    }
     // pad and sort descending (bitonic over 256)
     for (int i = threadIdx.x; i < CAND_MAX; i += blockDim.x)
         if (i >= k) picked[i] = 0ull;
@@ -191,20 +313,29 @@ sample_temperature_kernel(const float* __restrict__ logits, const float* __restr
     const float* row = logits + (long long)r * row_stride;
     const float inv_t = 1.0f / temperature[r];
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v == v) m = fmaxf(m, v);
-    }
+    for_each_logit(row, vocab, [&](float v, int) { if (v == v) m = fmaxf(m, v); });
     m = warp_max(m);
     if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = m;
     __syncthreads();
     m = (threadIdx.x & 31) < ((blockDim.x + 31) >> 5) ? redf[threadIdx.x & 31] : -INFINITY;
     m = warp_max(m);
 
-    const int per = (vocab + blockDim.x - 1) / blockDim.x;
+    // stretches of whole float4s, so that a thread reads its stretch sixteen bytes at a time
+    const int per = ((vocab + blockDim.x - 1) / blockDim.x + 3) & ~3;
     const int lo = min(vocab, (int)threadIdx.x * per), hi = min(vocab, lo + per);
     double s = 0.0;
-    for (int i = lo; i < hi; ++i) {
+    int i = lo;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+#pragma unroll 8
+        for (; i + 4 <= hi; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            if (v.x == v.x) s += (double)expf((v.x - m) * inv_t);
+            if (v.y == v.y) s += (double)expf((v.y - m) * inv_t);
+            if (v.z == v.z) s += (double)expf((v.z - m) * inv_t);
+            if (v.w == v.w) s += (double)expf((v.w - m) * inv_t);
+        }
+    }
+    for (; i < hi; ++i) {
         const float v = row[i];
         if (v == v) s += (double)expf((v - m) * inv_t);
     }
@@ -276,7 +407,7 @@ AXON_API int axon_topk(const float* logits, const int32_t* ks, float* cand_logit
                        int rows, int vocab, long long row_stride, cudaStream_t stream) {
     if (rows <= 0) return AXON_OK;
     if (vocab <= 0) { set_error("axon_topk: empty rows"); return AXON_BAD_ARGUMENT; }
-    topk_kernel<<<rows, 1024, 0, stream>>>(logits, ks, cand_logit, cand_id, vocab, row_stride);
+    topk_kernel<<<rows, 1024, 32 * 1024, stream>>>(logits, ks, cand_logit, cand_id, vocab, row_stride);
     return launch_status("axon_topk");
 }
 

@@ -164,15 +164,18 @@ def pick_tokens(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
         for i, t in zip(greedy, best.tolist()):
             out[i] = int(t)
     if plain:
-        sub = logits[torch.tensor(plain, device=dev)].contiguous()
-        temps = torch.tensor([rows[i].cfg.temp for i in plain], dtype=torch.float32, device=dev)
-        us = torch.tensor([rows[i].host.uniform() for i in plain], dtype=torch.float64, device=dev)
+        sub = logits if len(plain) == n else logits[torch.tensor(plain, device=dev)].contiguous()
+        # temperatures and uniforms in one host-to-device copy (each small copy costs a synchronisation)
+        both = torch.tensor([[rows[i].cfg.temp for i in plain], [rows[i].host.uniform() for i in plain]],
+                            dtype=torch.float64, device=dev)
+        temps, us = both[0].float(), both[1].contiguous()
         picked = torch.empty(len(plain), dtype=torch.int32, device=dev)
         ops.sample_temperature(sub, temps, us, picked)
         for i, t in zip(plain, picked.tolist()):
             out[i] = int(t)
     if cand:
-        sub = logits[torch.tensor(cand, device=dev)].contiguous()   # a copy: the penalty writes into it
+        # a copy: the penalty writes into it
+        sub = logits.clone() if len(cand) == n else logits[torch.tensor(cand, device=dev)].contiguous()
         host = lib.host()
         id_lists = []
         for i in cand:
@@ -191,10 +194,11 @@ def pick_tokens(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
         if on_device:
             kt = torch.tensor([ks[j] if j in set(on_device) else 0 for j in range(len(cand))],
                               dtype=torch.int32, device=dev)
-            cl = torch.empty((len(cand), kmax), dtype=torch.float32, device=dev)
-            ci = torch.empty((len(cand), kmax), dtype=torch.int32, device=dev)
+            both = torch.empty((2, len(cand), kmax), dtype=torch.int32, device=dev)   # logits and ids: one copy back
+            cl, ci = both[0].view(torch.float32), both[1]
             ops.topk(sub, kt, cl, ci)
-            cl_h, ci_h = cl.cpu().numpy(), ci.cpu().numpy()
+            both_h = both.cpu().numpy()
+            cl_h, ci_h = both_h[0].view(np.float32), both_h[1]
             for j in on_device:
                 k = min(ks[j], vocab)
                 out[cand[j]] = int(rows[cand[j]].host.pick(cl_h[j, :k], ci_h[j, :k]))

@@ -282,6 +282,43 @@ def test_topk_and_penalty(ops, vocab):
     assert bool(same[untouched].all())
 
 
+def test_topk_when_thousands_of_logits_share_their_top_byte(ops):
+    """More values in the deciding top byte than the kernel pools in shared memory (a flat row; a row
+    of nearly equal values): the general eight-pass selection takes over.  Same rule: larger id first."""
+    vocab = 152064
+    logits = torch.zeros(3, vocab, dtype=torch.float32, device=DEV)
+    logits[1] = 1.0 + rand(vocab, seed=53, std=1e-3)              # all within one top byte
+    logits[2] = rand(vocab, seed=54, std=3.0)
+    logits[2, 1000:90000] = 2.5                                   # 89,000 equal values among the largest
+    ks = torch.tensor([40, 256, 100], dtype=torch.int32, device=DEV)
+    cl = torch.empty(3, 256, dtype=torch.float32, device=DEV)
+    ci = torch.empty(3, 256, dtype=torch.int32, device=DEV)
+    ops.topk(logits, ks, cl, ci)
+    assert ci[0, :40].tolist() == list(range(vocab - 1, vocab - 41, -1))
+    for r in (1, 2):
+        k = int(ks[r])
+        key = logits[r].double().cpu()
+        top = torch.topk(key, 2000).indices.tolist()                # a superset of the k best, then the exact rule
+        order = sorted(set(top) | set(range(89999, 89999 - 300, -1)), key=lambda i: (key[i].item(), i), reverse=True)[:k]
+        assert ci[r, :k].tolist() == order
+        assert torch.equal(cl[r, :k].cpu(), logits[r].cpu()[order])
+
+
+def test_sample_temperature_large_rows(ops):
+    """The same inverse CDF over a vocabulary of 152,064 (float4 reads of each thread's stretch)."""
+    vocab, rows = 152064, 256
+    p = torch.softmax(rand(vocab, seed=55, std=4.0).double(), 0)
+    logits = torch.log(p).float().repeat(rows, 1).contiguous()
+    temps = torch.full((rows,), 1.0, dtype=torch.float32, device=DEV)
+    us = torch.rand(rows, generator=torch.Generator().manual_seed(2), dtype=torch.float64).to(DEV)
+    picked = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, temps, us, picked)
+    cdf = torch.cumsum(p, 0)
+    want = torch.searchsorted(cdf, us * cdf[-1], right=True).clamp(max=vocab - 1)
+    agree = (picked.long() == want).float().mean().item()
+    assert agree > 0.98, f"only {agree:.4f} of the picks match the inverse CDF"
+
+
 def test_sample_temperature(ops):
     vocab = 1000
     p = torch.softmax(rand(vocab, seed=52, std=2.0).double(), 0)
