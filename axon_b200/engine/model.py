@@ -61,9 +61,20 @@ class DecoderModel:
         return entry if e.cache_of is None else e.cache_of
 
     def graph_key(self, ctx: StepContext):
-        """The parts' host-side launch parameters for this step (see ``Part.graph_key``), once each."""
+        """The parts' host-side launch parameters for this step (see ``Part.graph_key``), once each.
+        Layers of one shape (kind, sizes and constants, nested parts) are asked once: this runs
+        on the host before every step of single tokens."""
+        reps = self.__dict__.get("_key_parts")
+        if reps is None:
+            seen, reps = set(), [self.embedding, self.final_norm, self.head]
+            for layer, block in zip(self.spec.layers, self.blocks):
+                sig = _shape_of(PartSpec(layer.block, layer.params, {}, layer.parts))
+                if sig not in seen:
+                    seen.add(sig)
+                    reps.append(block)
+            self._key_parts = reps
         keys = set()
-        for part in [self.embedding, self.final_norm, self.head, *self.blocks]:
+        for part in reps:
             keys.update(part.graph_key(ctx))
         return tuple(sorted(keys, key=repr))
 
@@ -98,6 +109,12 @@ class DecoderModel:
             logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         self.head.forward(h, logits)
         return logits
+
+
+def _shape_of(spec: PartSpec):
+    """What a part is apart from its weights: kind, parameters, and the same of its nested parts."""
+    return (spec.kind, repr(sorted(spec.params.items(), key=lambda kv: kv[0])),
+            tuple((name, _shape_of(sub)) for name, sub in sorted(spec.parts.items())))
 
 
 def _category_of(nested: Dict[str, str], parent: PartSpec, sub: PartSpec) -> str:
