@@ -206,8 +206,10 @@ def main() -> int:
                 "launches": launches, "bytes": weight_bytes + b * ctx_mid * kv_bytes_per_pos,
                 "clocks": sampler.summary() if sampler else None}
 
-    def time_prefill(T, repeats=3):
-        """One request, T tokens in one step; the best of the repeats after the first."""
+    def time_prefill(T, repeats=6):
+        """One request, T tokens in one step; the best of the repeats after the first.  (The
+        engine captures a portion size it meets a second time into a CUDA graph and replays it
+        from the third; a graph's first replay still carries its upload.)"""
         ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
         pms = []
         for it in range(repeats):
