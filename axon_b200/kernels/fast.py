@@ -96,7 +96,8 @@ DEFER_FOLD = os.environ.get("AXON_DEFER_FOLD", "1") != "0"
 
 
 def _gemm_small(a, w, bias, out, epi, M, N, K, defer: bool = False):
-    """At most 64 rows: the swapped tcgen05 kernel, else the mma.sync one.  With ``defer`` a
+    """Few rows (``_takes_swapped_kernel``): the swapped tcgen05 kernel, or for at most 64 rows the
+    mma.sync one when that is switched off.  With ``defer`` a
     split product returns a PendingFold instead of folding its partial sums itself."""
     if ENABLED["gemm_tc_small"] and not (M <= 8 and N <= MMA_SYNC_MAX_ROWS):
         partial, counters, _ = _split_scratch(a.device)
@@ -114,7 +115,7 @@ def _gemm_small(a, w, bias, out, epi, M, N, K, defer: bool = False):
             _OUTSTANDING[a.device] = owed
             return owed
         return True
-    if ENABLED["gemm_small_m"]:
+    if ENABLED["gemm_small_m"] and M <= SMALL_M:
         check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                            out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
         return True
