@@ -2,7 +2,8 @@
 toy architecture defined here (a mixer with state of its own, a windowed attention
 with adjacent-pair rotation, a layer that runs twice, a layer that reads another
 layer's cache) is registered, written as a random model folder, built and stepped
-without a change to the framework's files."""
+without a change to the framework's files; so is a second one with a feed-forward that
+routes tokens to experts and a position encoding of its own."""
 
 import math
 from dataclasses import dataclass
@@ -346,3 +347,220 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
     # a second request in the same slot starts from zeroed state
     got = rp.run_step({"step": 9, "entries": [{"id": "c", "tokens": seqs["b"][:7], "want": [6]}], "end": ["c"]})
     close(got, want["b"][6:7], tol, "state is zeroed for a new request")
+
+
+# ---------------------------------------------------------------------------
+# A second toy architecture: a feed-forward that routes each token to one of several experts,
+# and a position encoding of its own, both defined here.  Neither declares itself safe for CUDA
+# graphs, so its steps run eagerly.
+
+def register_routed_toy():
+    from axon_b200.config.base import ModelConfig, register_architecture
+    from axon_b200.kernels import linear as kernels_linear
+    from axon_b200.parts import FeedForward, LayerSpec, ModelSpec, Part, PartSpec, ScheduleEntry, TensorDecl, register_part
+
+    @register_part
+    class StretchedRotary(Part):
+        """Pair i of the first ``rot`` elements of a head, (i, i + rot/2), turns by
+        ``(pos / stretch) * base^(-i / (rot/2))``; the rest of the head passes unchanged."""
+        category, kind = "position", "toy_stretched_rotary"
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            p = spec.params
+            self.rot, self.adjacent = int(p["rot"]), False
+            self.stretch, self.base = float(p["stretch"]), float(p["base"])
+
+        def rotation(self, ctx):
+            key = ("toy_stretched_rotary", self.rot, self.stretch, self.base)
+            table = ctx.scratch.get(key)
+            if table is None:
+                ang = stretched_angles(ctx.host_positions, self.rot, self.stretch, self.base)
+                table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().to(self.rt.device)
+                ctx.scratch[key] = table
+            return table
+
+    @register_part
+    class Top1Experts(FeedForward):
+        """Router logits ``R h`` in float32; the token goes to the expert with the largest one
+        (the first among equals), whose output is ``W_out relu(W_in h)``."""
+        category, kind = "ffn", "toy_top1_experts"
+
+        @classmethod
+        def tensors(cls, spec):
+            p = spec.params
+            e, d, f = p["experts"], p["hidden_size"], p["expert_size"]
+            return {"router": TensorDecl((e, d)), "w_in": TensorDecl((e * f, d)), "w_out": TensorDecl((e * d, f))}
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            p = spec.params
+            self.e, self.d, self.f = int(p["experts"]), int(p["hidden_size"]), int(p["expert_size"])
+            self.router = tensors["router"]
+            self.w_in = tensors["w_in"].view(self.e, self.f, self.d)
+            self.w_out = tensors["w_out"].view(self.e, self.d, self.f)
+            self.seen = set()
+
+        def compute(self, h, ctx):
+            rt = self.rt
+            logits = torch.empty(h.shape[0], self.e, dtype=torch.float32, device=h.device)
+            kernels_linear.linear(h, self.router, logits, precise=rt.precise)
+            choice = logits.argmax(dim=-1)
+            out = torch.zeros(h.shape[0], self.d, dtype=torch.float32, device=h.device)
+            for e in range(self.e):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                self.seen.add(e)
+                mid = torch.empty(rows.numel(), self.f, dtype=rt.dtype, device=h.device)
+                kernels_linear.linear(h[rows].contiguous(), self.w_in[e], mid, precise=rt.precise)
+                part = torch.empty(rows.numel(), self.d, dtype=torch.float32, device=h.device)
+                kernels_linear.linear(mid.clamp_(min=0), self.w_out[e], part, precise=rt.precise)
+                out[rows] = part
+            return out
+
+    @dataclass(frozen=True)
+    class RoutedToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "RoutedToyForCausalLM"
+        model_types: ClassVar[Tuple[str, ...]] = ("routed_toy_test",)
+        hidden_size: int = 48
+        vocab_size: int = 77
+        heads: int = 3
+        kv_heads: int = 1
+        head_dim: int = 32
+        rot: int = 12
+        stretch: float = 2.5
+        base: float = 500.0
+        experts: int = 3
+        expert_size: int = 24
+        layers: int = 2
+        eps: float = 1e-6
+        max_positions: int = 80
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg})
+
+    def routed_spec(c):
+        norm = lambda name: PartSpec("rmsnorm", {"size": c.hidden_size, "eps": c.eps}, {"gain": name})
+
+        def layer(i):
+            mixer = PartSpec("attention", {"hidden_size": c.hidden_size, "heads": c.heads, "kv_heads": c.kv_heads,
+                                           "head_dim": c.head_dim, "qkv_bias": True, "out_bias": False,
+                                           "window": None, "scale": None},
+                             {k: f"l{i}.attn.{k}" for k in ("q", "k", "v", "o", "q_bias", "k_bias", "v_bias")},
+                             {"position": PartSpec("toy_stretched_rotary", {"rot": c.rot, "stretch": c.stretch, "base": c.base})})
+            ffn = PartSpec("toy_top1_experts", {"experts": c.experts, "hidden_size": c.hidden_size, "expert_size": c.expert_size},
+                           {k: f"l{i}.experts.{k}" for k in ("router", "w_in", "w_out")})
+            return LayerSpec("prenorm", {"norm_mixer": norm(f"l{i}.n1"), "mixer": mixer, "norm_ffn": norm(f"l{i}.n2"), "ffn": ffn})
+        return ModelSpec("RoutedToyForCausalLM", c.hidden_size, c.vocab_size, c.max_positions,
+                         PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"table": "embed"}),
+                         tuple(layer(i) for i in range(c.layers)), tuple(ScheduleEntry(i) for i in range(c.layers)),
+                         norm("final"),
+                         PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"weight": "head"}))
+
+    register_architecture(RoutedToyConfig, routed_spec)
+    return RoutedToyConfig
+
+
+def stretched_angles(positions, rot, stretch, base):
+    pairs = rot // 2
+    freq = torch.tensor([base ** (-i / pairs) for i in range(pairs)], dtype=torch.float64)
+    return torch.tensor(list(positions), dtype=torch.float64)[:, None] / stretch * freq[None, :]
+
+
+def decisive_routing(c, w):
+    """Random routers decide most tokens by a hair, which bfloat16 would turn the other way.  So
+    two coordinates of the residual carry two bits of the token id, large against everything a
+    layer adds, and each router reads its three logits off those two: every decision has a margin."""
+    ids = torch.arange(c.vocab_size)
+    w["embed"][:, 0] = 4.0 * (1 - 2 * (ids & 1)).double()
+    w["embed"][:, 1] = 4.0 * (1 - 2 * ((ids >> 1) & 1)).double()
+    for i in range(c.layers):
+        w[f"l{i}.n2"][:2] = 1.0
+        r = w[f"l{i}.experts.router"]
+        r *= 0.25
+        r[0, 0] += 1.0; r[0, 1] += 1.0          # both bits clear
+        r[1, 0] += 1.0; r[1, 1] -= 1.0          # the second bit set
+        r[2, 0] -= 1.0                          # the first bit set
+
+
+def routed_plain_forward(c, w, tokens):
+    """The routed toy written with the plain functions; also each routed decision's margin
+    (largest router logit minus the next) and the experts chosen."""
+    T = len(tokens)
+    x = plain.embed(w["embed"], tokens)
+    ang = stretched_angles(range(T), c.rot, c.stretch, c.base)
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def turn(v):
+        half = c.rot // 2
+        a, b = v[..., :half], v[..., half:c.rot]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, v[..., c.rot:]], dim=-1)
+    margins, chosen = [], []
+    for i in range(c.layers):
+        p = f"l{i}.attn."
+        h = plain.rms_norm(x, w[f"l{i}.n1"], c.eps)
+        q = plain.linear(h, w[p + "q"], w[p + "q_bias"]).view(T, c.heads, c.head_dim)
+        k = plain.linear(h, w[p + "k"], w[p + "k_bias"]).view(T, c.kv_heads, c.head_dim)
+        v = plain.linear(h, w[p + "v"], w[p + "v_bias"]).view(T, c.kv_heads, c.head_dim)
+        o = plain.causal_gqa_attention(turn(q), turn(k), v).reshape(T, c.heads * c.head_dim)
+        x = x + plain.linear(o, w[p + "o"])
+        h = plain.rms_norm(x, w[f"l{i}.n2"], c.eps)
+        logits = plain.linear(h, w[f"l{i}.experts.router"])
+        top = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(top[:, 0] - top[:, 1])
+        choice = logits.argmax(dim=-1)
+        chosen.append(choice)
+        w_in = w[f"l{i}.experts.w_in"].view(c.experts, c.expert_size, c.hidden_size)
+        w_out = w[f"l{i}.experts.w_out"].view(c.experts, c.hidden_size, c.expert_size)
+        y = torch.stack([plain.linear(torch.relu(plain.linear(h[t:t + 1], w_in[e])), w_out[e])[0]
+                         for t, e in enumerate(choice.tolist())])
+        x = x + y
+    return plain.linear(plain.rms_norm(x, w["final"], c.eps), w["head"]), torch.stack(margins), torch.stack(chosen)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path, dtype):
+    from safetensors.torch import load_file
+
+    from axon_b200.engine.build import build_engine
+    from axon_b200.engine.replay import Replayer
+    from axon_b200.weights import write_random_model, write_safetensors
+    cfg = register_routed_toy()()
+    folder = str(tmp_path / "routed")
+    write_random_model(folder, cfg, seed=11, std=0.12)
+    stored = load_file(folder + "/model.safetensors")
+    w = {k: v.double() for k, v in stored.items()}
+    decisive_routing(cfg, w)
+    write_safetensors(folder + "/model.safetensors", {k: v.to(stored[k].dtype) for k, v in w.items()}, {"format": "pt"})
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    g = torch.Generator().manual_seed(4)
+    seqs = {r: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for r, n in (("a", 37), ("b", 26))}
+    want, margins, chosen = {}, [], []
+    for r, t in seqs.items():
+        want[r], m, ch = routed_plain_forward(cfg, w, t)
+        margins.append(m.flatten()); chosen.append(ch.flatten())
+    assert float(torch.cat(margins).min()) > 1.0, "the routing of this test is not decisive"
+    assert sorted(set(torch.cat(chosen).tolist())) == list(range(cfg.experts)), "an expert is never chosen"
+
+    engine = build_engine(folder, dtype=dtype, page_size=4, max_tokens=128, max_slots=2, max_positions=cfg.max_positions,
+                          shuffle_seed=6)
+    assert not engine.model.graph_safe            # parts that say nothing about graphs keep the steps eager
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    rp, fed = Replayer(engine), {"a": 0, "b": 0}
+    plan = [[("a", 11)], [("a", 2), ("b", 7)], [("a", 1), ("b", 1)], [("b", 1), ("a", 1)], [("b", 17)], [("a", 22)]]
+    for k, row in enumerate(plan):
+        ents, rows = [], []
+        for r, n in row:
+            t = seqs[r][fed[r]:fed[r] + n]
+            ents.append({"id": r, "tokens": t, "want": list(range(len(t)))})
+            rows += [want[r][fed[r] + j] for j in range(len(t))]
+            fed[r] += len(t)
+        got = rp.run_step({"step": k, "entries": ents, "end": [r for r, _ in row if fed[r] == len(seqs[r])]})
+        close(got, torch.stack(rows), tol, f"routed toy, step {k}")
+    assert fed == {r: len(t) for r, t in seqs.items()}
+    for block in engine.model.blocks:
+        assert block.ffn.seen == set(range(cfg.experts))
+    engine.cache.flush()
+    engine.cache.manager.check()
