@@ -3,7 +3,8 @@ toy architecture defined here (a mixer with state of its own, a windowed attenti
 with adjacent-pair rotation, a layer that runs twice, a layer that reads another
 layer's cache) is registered, written as a random model folder, built and stepped
 without a change to the framework's files; so is a second one with a feed-forward that
-routes tokens to experts and a position encoding of its own."""
+routes tokens to experts and a position encoding of its own, and a third with a norm and a
+block arrangement of its own."""
 
 import math
 from dataclasses import dataclass
@@ -564,3 +565,177 @@ def test_toy_routed_feed_forward_and_position_encoding(tmp_path, dtype):
         assert block.ffn.seen == set(range(cfg.experts))
     engine.cache.flush()
     engine.cache.manager.check()
+
+
+# ---------------------------------------------------------------------------
+# A third toy: a norm and a block arrangement of their own, wide enough (512) that the products
+# for few rows are split over K and leave their sums to the next reader.  Neither toy part knows
+# of owed sums, so their callers have to fold first.
+
+def register_wide_toy():
+    from axon_b200.config.base import ModelConfig, register_architecture
+    from axon_b200.parts import LayerSpec, ModelSpec, Part, PartSpec, ScheduleEntry, TensorDecl, register_part
+
+    @register_part
+    class CenteredNorm(Part):
+        """``(x - mean) / sqrt(var + eps) * gain`` over a row."""
+        category, kind = "norm", "toy_centered_norm"
+
+        @classmethod
+        def tensors(cls, spec):
+            return {"gain": TensorDecl((spec.params["size"],), "gain")}
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            self.gain, self.eps = tensors["gain"], float(spec.params["eps"])
+
+        def forward(self, x, out, rows=None):
+            src = x if rows is None else x[rows.long()]
+            mu = src.mean(-1, keepdim=True)
+            var = ((src - mu) ** 2).mean(-1, keepdim=True)
+            out.copy_(((src - mu) / torch.sqrt(var + self.eps) * self.gain.float()).to(out.dtype))
+
+    @register_part
+    class ParallelBlock(Part):
+        """``x += mixer(norm(x)) + ffn(norm(x))``: both read the same normed rows."""
+        category, kind = "block", "toy_parallel"
+        nested = {"norm": "norm", "mixer": "mixer", "ffn": "ffn"}
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            self.norm, self.mixer, self.ffn = (build(spec.parts[k]) for k in ("norm", "mixer", "ffn"))
+
+        def forward(self, x, ctx, cache, write_cache=True):
+            h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            self.norm.forward(x, h)
+            self.mixer.forward(h, x, ctx, cache, write_cache)
+            self.ffn.forward(h, x, ctx)
+
+    @dataclass(frozen=True)
+    class WideToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "WideToyForCausalLM"
+        model_types: ClassVar[Tuple[str, ...]] = ("wide_toy_test",)
+        hidden_size: int = 512
+        vocab_size: int = 131
+        heads: int = 4
+        kv_heads: int = 2
+        head_dim: int = 128
+        ffn: int = 1024
+        theta: float = 3e4
+        eps: float = 1e-4
+        max_positions: int = 96
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg})
+
+    def wide_spec(c):
+        norm = lambda name: PartSpec("toy_centered_norm", {"size": c.hidden_size, "eps": c.eps}, {"gain": name})
+
+        def attn(p):
+            return PartSpec("attention", {"hidden_size": c.hidden_size, "heads": c.heads, "kv_heads": c.kv_heads,
+                                          "head_dim": c.head_dim, "qkv_bias": True, "out_bias": False,
+                                          "window": None, "scale": None},
+                            {k: f"{p}.{k}" for k in ("q", "k", "v", "o", "q_bias", "k_bias", "v_bias")},
+                            {"position": PartSpec("rope", {"head_dim": c.head_dim, "theta": c.theta, "pairing": "half"})})
+
+        def ffn(p):
+            return PartSpec("swiglu", {"hidden_size": c.hidden_size, "intermediate_size": c.ffn},
+                            {k: f"{p}.{k}" for k in ("gate", "up", "down")})
+        layers = (
+            LayerSpec("prenorm", {"norm_mixer": norm("l0.n1"), "mixer": attn("l0.attn"),
+                                  "norm_ffn": norm("l0.n2"), "ffn": ffn("l0.ffn")}),
+            LayerSpec("toy_parallel", {"norm": norm("l1.n"), "mixer": attn("l1.attn"), "ffn": ffn("l1.ffn")}),
+            LayerSpec("prenorm", {"norm_mixer": norm("l2.n1"), "mixer": attn("l2.attn"),
+                                  "norm_ffn": norm("l2.n2"), "ffn": ffn("l2.ffn")}),
+        )
+        return ModelSpec("WideToyForCausalLM", c.hidden_size, c.vocab_size, c.max_positions,
+                         PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"table": "embed"}),
+                         layers, tuple(ScheduleEntry(i) for i in range(3)), norm("final"),
+                         PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"weight": "head"}))
+
+    register_architecture(WideToyConfig, wide_spec)
+    return WideToyConfig
+
+
+def wide_plain_forward(c, w, tokens):
+    T = len(tokens)
+    pos = list(range(T))
+
+    def norm(x, name):
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        return (x - mu) / torch.sqrt(var + c.eps) * w[name]
+
+    def attn(h, p):
+        q = plain.linear(h, w[p + ".q"], w[p + ".q_bias"]).view(T, c.heads, c.head_dim)
+        k = plain.linear(h, w[p + ".k"], w[p + ".k_bias"]).view(T, c.kv_heads, c.head_dim)
+        v = plain.linear(h, w[p + ".v"], w[p + ".v_bias"]).view(T, c.kv_heads, c.head_dim)
+        q, k = plain.rope_half(q, pos, c.theta), plain.rope_half(k, pos, c.theta)
+        o = plain.causal_gqa_attention(q, k, v).reshape(T, c.heads * c.head_dim)
+        return plain.linear(o, w[p + ".o"])
+
+    def ffn(h, p):
+        return plain.swiglu_ffn(h, w[p + ".gate"], w[p + ".up"], w[p + ".down"])
+
+    def prenorm(x, i):
+        x = x + attn(norm(x, f"l{i}.n1"), f"l{i}.attn")
+        return x + ffn(norm(x, f"l{i}.n2"), f"l{i}.ffn")
+    x = prenorm(plain.embed(w["embed"], tokens), 0)
+    h = norm(x, "l1.n")
+    x = x + attn(h, "l1.attn") + ffn(h, "l1.ffn")
+    x = prenorm(x, 2)
+    return plain.linear(norm(x, "final"), w["head"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_norm_and_block_between_products_that_leave_sums_owed(tmp_path, dtype, monkeypatch):
+    from safetensors.torch import load_file
+
+    from axon_b200.engine.build import build_engine
+    from axon_b200.engine.replay import Replayer
+    from axon_b200.kernels import fast
+    from axon_b200.weights import write_random_model
+    cfg = register_wide_toy()()
+    folder = str(tmp_path / "wide")
+    write_random_model(folder, cfg, seed=21, std=0.04)
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    g = torch.Generator().manual_seed(8)
+    seqs = {r: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for r, n in (("a", 45), ("b", 30))}
+    want = {r: wide_plain_forward(cfg, w, t) for r, t in seqs.items()}
+    # count the products that left their sums to a reader, and the separate folds that paid them
+    owed_made, folds_run = [], []
+    if dtype == "bfloat16":
+        from axon_b200.kernels import ops
+        make, fold = fast.PendingFold.__init__, ops.fold_partials
+
+        def counted_init(self, *a, **k):
+            owed_made.append(1)
+            make(self, *a, **k)
+
+        def counted_fold(pending):
+            folds_run.append(1)
+            return fold(pending)
+        monkeypatch.setattr(fast.PendingFold, "__init__", counted_init)
+        monkeypatch.setattr(ops, "fold_partials", counted_fold)
+    engine = build_engine(folder, dtype=dtype, page_size=8, max_tokens=160, max_slots=2, max_positions=cfg.max_positions,
+                          shuffle_seed=3)
+    assert not engine.model.graph_safe
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    rp, fed = Replayer(engine), {"a": 0, "b": 0}
+    plan = [[("a", 13)], [("a", 1), ("b", 9)], [("a", 1), ("b", 1)], [("b", 20)], [("a", 2), ("b", 0)], [("a", 28)]]
+    for k, row in enumerate(plan):
+        ents, rows = [], []
+        for r, n in row:
+            if n == 0:
+                continue
+            t = seqs[r][fed[r]:fed[r] + n]
+            ents.append({"id": r, "tokens": t, "want": list(range(len(t)))})
+            rows += [want[r][fed[r] + j] for j in range(len(t))]
+            fed[r] += len(t)
+        got = rp.run_step({"step": k, "entries": ents, "end": [r for r, n in row if n and fed[r] == len(seqs[r])]})
+        close(got, torch.stack(rows), tol, f"wide toy, step {k}")
+    assert fed == {r: len(t) for r, t in seqs.items()}
+    if dtype == "bfloat16":
+        assert owed_made, "no product of this model left its sums to a reader: the sizes are too small for the test"
+        assert folds_run, "the toy norm's callers never folded for it"
