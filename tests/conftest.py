@@ -1,4 +1,4 @@
-"""Shared fixtures: the two tiny configurations, model folders made in temporary
+"""Shared fixtures: the tiny configurations, model folders made in temporary
 folders, and the ``gpu`` marker."""
 
 from __future__ import annotations
@@ -54,7 +54,16 @@ TINY_C = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 1024,
     "use_sliding_window": False, "hidden_act": "silu",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# A fourth one whose sizes no tuned kernel takes: head size 48, a width that is no multiple of
+# 8 (rows that are no whole 16-byte pieces), as many kv heads as heads, a prime vocabulary.
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 132, "vocab_size": 211, "rope_theta": 200000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 160,
+    "use_sliding_window": False, "hidden_act": "silu",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_folder(path: str, cfg: dict, seed: int, sharpen: float = 6.0) -> str:

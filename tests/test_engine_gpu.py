@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 # wrong formula moves logits by 1e-1 of the scale or more.
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
-PROMPT_LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 77], "C": [3, 33, 90, 130]}
+PROMPT_LENGTHS = {"A": [5, 17, 31, 70], "B": [1, 9, 40, 77], "C": [3, 33, 90, 130], "D": [2, 21, 66, 101]}
 
 
 def tokens_for(name, i, n):
@@ -110,7 +110,7 @@ class Trace:
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(model_folders, expected, name, dtype):
     engine = build(model_folders[name], dtype, max_tokens=256)
     for i, n in enumerate(PROMPT_LENGTHS[name]):
@@ -121,7 +121,7 @@ def test_each_request_alone_and_whole(model_folders, expected, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(model_folders, expected, name, dtype):
     engine = build(model_folders[name], dtype, max_tokens=256)
     for i in (2, 3):
@@ -137,7 +137,7 @@ def test_last_32_tokens_one_by_one(model_folders, expected, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("sizes", [[5, 30, 3, 17, 2, 1, 33], [24, 32, 31, 2, 47], [2, 2, 2, 16, 1, 64], [16, 16, 16, 16]])
 def test_portions_of_changing_size(model_folders, expected, name, dtype, sizes):
     engine = build(model_folders[name], dtype, max_tokens=256, page_size=16)
@@ -202,7 +202,7 @@ def mixed_trace(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("shuffle", [0, 11])
 def test_mixed_batches_with_pages_used_again(model_folders, plain_models, name, dtype, shuffle):
     tr, keys = mixed_trace(name)
