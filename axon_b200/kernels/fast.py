@@ -182,10 +182,16 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
 
 FA_HEAD_DIMS = (16, 32, 64, 128)
 FA_MAX_SPLITS = 32
-#: CTAs the decode attention aims at (and does not exceed) when it splits the keys of each request:
-#: two CTAs fit an SM, and a launch that spills into a second wave pays for it (measured at 7B
-#: sizes: 320 CTAs at batch 16 cost 10 % of the step against 256)
-FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 256))
+#: CTAs the decode attention never exceeds when it splits the keys of each request: two CTAs fit
+#: an SM, and a launch that spills into a second wave pays for it (measured at 7B sizes: 320 CTAs
+#: at batch 16 cost 10 % of the step against 256)
+FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 2 * 148))
+#: the split rule's model, in units of one key tile's time in a CTA: what each further share adds to
+#: the fold, and what the fold's kernel costs when there is one
+FA_SPLIT_COST = float(os.environ.get("AXON_FA_SPLIT_COST", 0.15))
+FA_FOLD_COST = float(os.environ.get("AXON_FA_FOLD_COST", 2.0))
+#: launches of more CTAs than this pay a further tile's time in the model
+FA_ROOMY_CTAS, FA_CROWD_COST = 256, 1.0
 #: whether the last split folds the partials itself (else a second kernel does; measured at 7B
 #: sizes the second kernel is a little faster up to batch 8 and equal at 64, because it overlaps
 #: with the kernels around it while the in-kernel fold lengthens the slowest CTA)
@@ -236,17 +242,33 @@ def _attention_items(ctx, group: int, pre_rows: int = 64):
     return got
 
 
+def _key_splits(pairs: int, tiles: int) -> int:
+    """Into how many shares to cut the keys of each of ``pairs`` (request, kv head) whose longest
+    context has ``tiles`` key tiles.  All CTAs must fit at once (``FA_TARGET_CTAS``); among the
+    counts that do, the cheapest by a small model: the key tiles of the longest share, plus what
+    every further share costs the fold, plus the fold's own kernel when there is more than one, plus
+    a little when the launch takes nearly every place on the GPU.  Measured at 7B sizes and 2,048 keys:
+    against "as many shares as fit in 256 CTAs" the step is 2 % faster at batch 24 (3 shares instead
+    of 2) and 7 % at batch 36 (2 instead of 1), and the same at batches 1 to 16; 288 CTAs instead of
+    256 at batch 8 (9 shares of 4 tiles instead of 8 of 5) was 1.3 % slower, hence the last term."""
+    most = max(1, min(tiles, FA_MAX_SPLITS, FA_TARGET_CTAS // max(pairs, 1)))
+    best, best_cost = 1, float(tiles)
+    for s in range(2, most + 1):
+        cost = -(-tiles // s) + FA_SPLIT_COST * s + FA_FOLD_COST + (FA_CROWD_COST if pairs * s > FA_ROOMY_CTAS else 0.0)
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def decode_split_count(n_dec: int, kv_heads: int, max_kv_len: int) -> int:
     """Into how many shares the decode attention cuts each request's keys: the one launch
     parameter of a step of single tokens that depends on the contexts' lengths."""
-    tiles = -(-max_kv_len // 64)
-    return max(1, min(tiles, FA_MAX_SPLITS, FA_TARGET_CTAS // (n_dec * kv_heads)))
+    return _key_splits(n_dec * kv_heads, -(-max_kv_len // 64))
 
 
 def _decode_splits(n_dec: int, kv, tiles: int, rt):
     """Key splits for the decode shape and the scratch their partials go to (None: a cluster folds)."""
-    target = FA_TARGET_CTAS
-    splits = max(1, min(tiles, FA_MAX_SPLITS, target // (n_dec * kv.kv_heads)))
+    splits = _key_splits(n_dec * kv.kv_heads, tiles)
     scratch = None
     # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
     # no second kernel); longer contexts keep more, independent splits
@@ -255,7 +277,7 @@ def _decode_splits(n_dec: int, kv, tiles: int, rt):
     elif splits > 1:
         # sized for the most splits this batch can get, so that the buffer never moves
         # while the contexts grow (captured graphs hold its address)
-        most = max(1, min(FA_MAX_SPLITS, target // (n_dec * kv.kv_heads)))
+        most = max(1, min(FA_MAX_SPLITS, FA_TARGET_CTAS // (n_dec * kv.kv_heads)))
         scratch = rt.buffer("fa_scratch", (n_dec * kv.kv_heads * most * 16 * (kv.head_dim + 2),), torch.float32)
     return splits, scratch
 

@@ -15,8 +15,12 @@ def test_decode_attention_never_starts_more_ctas_than_fit():
     # the sizes of the measurement: 8 requests x 4 kv heads share 256 CTAs
     assert fast.decode_split_count(8, 4, 2048) == 8
     assert fast.decode_split_count(64, 4, 2048) == 1
-    assert fast.decode_split_count(1, 4, 2048) == 32
-    assert fast.decode_split_count(8, 4, 100) == 2          # no more shares than key tiles
+    assert fast.decode_split_count(1, 4, 2048) == 16        # 32 shares of one tile would only make the fold longer
+    assert fast.decode_split_count(8, 4, 100) == 1          # two tiles: a second kernel to fold them costs more
+    assert fast.decode_split_count(8, 4, 2080) == 7         # 33 tiles: 7 shares are as short as 8 (5 tiles)
+    # between 32 and 37 requests two shares still fit at once, and halve the longest CTA
+    assert fast.decode_split_count(36, 4, 2048) == 2 and fast.decode_split_count(24, 4, 2048) == 3
+    assert fast.decode_split_count(38, 4, 2048) == 1
 
 
 def test_which_products_take_the_swapped_kernel():
