@@ -304,7 +304,7 @@ def generate(net: Backend, cache: BackendCache, prompt: Sequence[int], logits, o
             ops.argmax(row.contiguous(), best)
             nxt = int(best.item())
         else:
-            nxt = pick_tokens(row.contiguous().clone(), [sampler])[0]
+            nxt = pick_tokens(row.contiguous(), [sampler])[0]      # (it copies what it changes)
         picks += 1
         if nxt in stop:
             break

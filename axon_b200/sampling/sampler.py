@@ -183,17 +183,22 @@ def pick_tokens(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
             ids = host.penalty_ids(rows[i].history, c.repeat_last_n) if (c.repeat_penalty != 1.0 and c.repeat_last_n > 0) else []
             id_lists.append(ids)
         width = max((len(x) for x in id_lists), default=0)
-        if width:
-            pid = np.full((len(cand), width), -1, dtype=np.int32)
-            for j, ids in enumerate(id_lists):
-                pid[j, :len(ids)] = ids
-            pen = torch.tensor([rows[i].cfg.repeat_penalty for i in cand], dtype=torch.float32, device=dev)
-            ops.repeat_penalty(sub, torch.from_numpy(pid).to(dev), pen)
         ks = [rows[i].cfg.top_k for i in cand]
         on_device = [j for j, k in enumerate(ks) if 0 < k <= kmax]
+        # the rows' k, penalty (float bits) and penalised ids in one host-to-device copy
+        # (each small copy costs a synchronisation)
+        nc = len(cand)
+        flat = np.full(nc * (2 + width), -1, dtype=np.int32)
+        keep = set(on_device)
+        flat[:nc] = [ks[j] if j in keep else 0 for j in range(nc)]
+        flat[nc:2 * nc] = np.asarray([rows[i].cfg.repeat_penalty for i in cand], dtype=np.float32).view(np.int32)
+        for j, ids in enumerate(id_lists):
+            flat[2 * nc + j * width: 2 * nc + j * width + len(ids)] = ids
+        flat_dev = torch.from_numpy(flat).to(dev)
+        if width:
+            ops.repeat_penalty(sub, flat_dev[2 * nc:].view(nc, width), flat_dev[nc:2 * nc].view(torch.float32))
         if on_device:
-            kt = torch.tensor([ks[j] if j in set(on_device) else 0 for j in range(len(cand))],
-                              dtype=torch.int32, device=dev)
+            kt = flat_dev[:nc]
             both = torch.empty((2, len(cand), kmax), dtype=torch.int32, device=dev)   # logits and ids: one copy back
             cl, ci = both[0].view(torch.float32), both[1]
             ops.topk(sub, kt, cl, ci)
