@@ -27,7 +27,7 @@ from .engine.build import build_engine, parse_dtype
 from .engine.step import Engine, StepEntry, StepError
 from .kernels import lib, ops
 from .sampling.sampler import RowSampler, SampleCfg, pick_tokens
-from .weights.loader import WeightsError, expected_tensors
+from .weights.loader import WeightsError, check_checkpoint
 from .weights.safetensors_io import Checkpoint
 
 #: most tokens of one request per prefill pass (the reference feeds prompts in passes too:
@@ -44,10 +44,8 @@ class Model:
     n_tensors: int
     n_params: int
     n_bytes: int
-
-    @property
-    def ctx_len(self) -> int:
-        return int(getattr(self.config, "max_position_embeddings", 0))
+    #: the longest request the model is made for (its spec's ``max_positions``)
+    ctx_len: int = 0
 
 
 def load(path: str, device: str = "cuda") -> Model:
@@ -56,23 +54,15 @@ def load(path: str, device: str = "cuda") -> Model:
     names the folder and says why it cannot be read or run (src/lib.rs:112-127)."""
     config = load_config(path)
     spec = architecture_of(config.to_dict()).build_spec(config)
-    want = expected_tensors(spec)
     ck = Checkpoint(path)
     try:
+        want = check_checkpoint(ck, spec, path)
         have = ck.infos
-        ignored = lambda n: any(n.endswith(s) for s in spec.ignored_suffixes)
-        missing = sorted(n for n in want if n not in have)
-        unexpected = sorted(n for n in have if n not in want and not ignored(n))
-        shapes = [(n, have[n].shape, want[n].shape) for n in sorted(want)
-                  if n in have and tuple(have[n].shape) != tuple(want[n].shape)]
-        dtypes = [(n, have[n].dtype) for n in sorted(want) if n in have and have[n].dtype not in ("BF16", "F16", "F32")]
-        if missing or unexpected or shapes or dtypes:
-            raise WeightsError(path, missing, unexpected, shapes, dtypes)
         params = sum(int(np.prod(have[n].shape)) for n in want)
         nbytes = sum(have[n].end - have[n].begin for n in want)
     finally:
         ck.close()
-    return Model(path, config, len(want), params, nbytes)
+    return Model(path, config, len(want), params, nbytes, int(spec.max_positions))
 
 
 @dataclass(frozen=True)
@@ -118,7 +108,9 @@ class BackendOptions:
         return replace(self, _parallel=int(n))
 
     def kv_tokens(self, n: int) -> "BackendOptions":
-        """Positions the cache pool holds over all live requests (default: max_ctx)."""
+        """Positions the cache pool holds over all live requests.  Default: what the device has
+        free once the weights are placed, and no more than ``parallel`` requests of ``max_ctx``
+        need (the reference sizes its pool so: src/serve.rs:2411-2449)."""
         return replace(self, _kv_tokens=int(n))
 
     def step_tokens(self, n: int) -> "BackendOptions":
@@ -184,7 +176,7 @@ class Backend:
         if engine is None:
             path = model.path if isinstance(model, Model) else model
             engine = build_engine(path, dtype=o._dtype, device=o._device, page_size=o._page_size,
-                                  max_tokens=o._kv_tokens or o._max_ctx, max_slots=o._parallel,
+                                  max_tokens=o._kv_tokens, max_slots=o._parallel,
                                   max_positions=o._max_ctx, max_step_tokens=o._step_tokens)
         self.engine = engine
         self.config = engine.config
@@ -254,7 +246,12 @@ class Backend:
         if len(tokens) != len(caches):
             raise StepError("decode_batch needs one token per cache")
         best = self.engine.step([StepEntry(c.slot, [int(t)], [0]) for c, t in zip(caches, tokens)], greedy=True)
-        return best.tolist()
+        picks = best.tolist()
+        # a kernel that gave up on a wait returns garbage without an error: ask now and then,
+        # where the host has just waited for the device anyway
+        if self.engine.steps % 512 == 0:
+            self.engine.check_device()
+        return picks
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], n_gen: Union[int, Sequence[int]],
                        stop: Sequence[int] = (), sample: Union[None, SampleCfg, Sequence[Optional[SampleCfg]]] = None,
@@ -321,4 +318,5 @@ def generate(net: Backend, cache: BackendCache, prompt: Sequence[int], logits, o
         st.passes += 1
     st.decided = picks
     st.forward = (count, secs)
+    net.engine.check_device()
     return st

@@ -90,20 +90,47 @@ class _Tok:
 
 
 def cmd_info(path: str) -> int:
+    """Architecture, sizes and tensors of a model folder (src/cli.rs:499-532).  Everything
+    printed comes from the model's spec and its configuration's own keys, whatever the
+    architecture calls them."""
     from . import api
+    from .cache.manager import bytes_per_token
     from .config.base import architecture_of
+    from .engine.model import layer_cache_needs
+    from .parts.spec import KvNeed, StateNeed
     from .weights.loader import expected_tensors
     from .weights.safetensors_io import Checkpoint
 
     m = api.load(path)
     c = m.config
-    print(f"{path}: {c.architecture}")
-    print(f"  layers {c.num_hidden_layers} / dim {c.hidden_size} / heads {c.num_attention_heads} "
-          f"(kv {c.num_key_value_heads}) / head_dim {c.head_dim} / ffn {c.intermediate_size} / vocab {c.vocab_size}")
-    print(f"  ctx {c.max_position_embeddings}, rope_theta {c.rope_theta:g}, rms_norm_eps {c.rms_norm_eps:g}, "
-          f"tied head: {'yes' if c.tie_word_embeddings else 'no'}")
-    print(f"  {m.n_tensors} tensors, {m.n_params:,} parameters, {m.n_bytes:,} bytes")
     spec = architecture_of(c.to_dict()).build_spec(c)
+    print(f"{path}: {spec.architecture}")
+    print(f"  layers {len(spec.layers)} (schedule of {len(spec.schedule)} runs) / dim {spec.hidden_size} / "
+          f"vocab {spec.vocab_size} / ctx {spec.max_positions}")
+    skip = ("architectures", "model_type")
+    print("  config: " + ", ".join(f"{k} {v:g}" if isinstance(v, float) else f"{k} {v}"
+                                   for k, v in sorted(c.to_dict().items()) if k not in skip))
+    kinds = {}
+    for l in spec.layers:
+        sig = l.block + "(" + ", ".join(f"{n}: {p.kind}" for n, p in sorted(l.parts.items())) + ")"
+        kinds[sig] = kinds.get(sig, 0) + 1
+    for sig, n in kinds.items():
+        print(f"  {n} x {sig}")
+    needs = [layer_cache_needs(spec.layers[e.layer]) if e.cache_of is None else {} for e in spec.schedule]
+    groups = {}
+    for entry in needs:
+        for need in entry.values():
+            groups[need] = groups.get(need, 0) + 1
+    for need, n in groups.items():
+        if isinstance(need, KvNeed):
+            rows = f"keys of {need.head_dim}" + (f" and values of {need.value_dim}" if need.planes == 2 else " (one plane)")
+            print(f"  cache: {n} runs keep {rows} x {need.kv_heads} kv heads per position"
+                  + (f", the last {need.window} positions" if need.window else ""))
+        elif isinstance(need, StateNeed):
+            print(f"  cache: {n} runs keep state {list(need.shape)} {need.dtype} per request")
+    import torch
+    print(f"  cache bytes per position: {bytes_per_token(needs, torch.bfloat16):,} (bfloat16)")
+    print(f"  {m.n_tensors} tensors, {m.n_params:,} parameters, {m.n_bytes:,} bytes")
     ck = Checkpoint(path)
     for name, decl in sorted(expected_tensors(spec).items()):
         info = ck.infos[name]

@@ -39,7 +39,6 @@ struct FaParams {
     PagedKv kv;
     int n_segments, heads, group, tokens_per_tile, n_splits, window;
     float scale_log2;            // scale * log2(e)
-    int cluster;                 // the splits of an (item, kv head) are one thread-block cluster and fold in shared memory
     // Decode steps may hand over the q/k/v product itself instead of rotated queries and a written
     // cache (qkv != nullptr): every CTA rotates its own queries, and the CTA whose keys include
     // the new positions rotates and writes their keys and values before it reads them.
@@ -139,6 +138,7 @@ template <int HD> struct KvLoader {
     const int32_t* bt;              // the request's row of the block table
     const __nv_bfloat16* src0;      // this thread's chunk of row 0 of the kv head in page 0 (K plane)
     long long page_stride, v_off;
+    PagedKv kvc;                    // for checked tables
     int ps, pages_per_tile, last_page, kv_len, r0;
     int in_page[ITER], page_of[ITER];
     uint32_t dst[ITER];
@@ -146,7 +146,7 @@ template <int HD> struct KvLoader {
     __device__ __forceinline__ void init(const __nv_bfloat16* pool, const PagedKv& kv, int slot, int kvh, int kv_len_) {
         const int c = threadIdx.x % CPR;
         r0 = threadIdx.x / CPR;
-        ps = kv.page_size; kv_len = kv_len_;
+        ps = kv.page_size; kv_len = kv_len_; kvc = kv;
         bt = kv.block_table + (long long)slot * kv.table_stride;
         src0 = pool + kv.entry_offset + (long long)kvh * ps * HD + c * 8;
         page_stride = kv.page_stride; v_off = kv.v_offset;
@@ -166,7 +166,7 @@ template <int HD> struct KvLoader {
             const int first = (key0 / FA_BN) * pages_per_tile;
 #pragma unroll
             for (int j = 0; j < ITER; ++j) {
-                const int page = bt[min(first + page_of[j], last_page)];
+                const int page = kvc.page(bt[min(first + page_of[j], last_page)]);
                 const __nv_bfloat16* src = src0 + (long long)page * page_stride + in_page[j];
                 cp_async16(k_tile + dst[j], src);
                 cp_async16(v_tile + dst[j], src + v_off);
@@ -175,7 +175,7 @@ template <int HD> struct KvLoader {
 #pragma unroll
             for (int j = 0; j < ITER; ++j) {
                 const int pos = min(key0 + r0 + RPP * j, kv_len - 1), lp = pos / ps;
-                const __nv_bfloat16* src = src0 + (long long)bt[lp] * page_stride + (pos - lp * ps) * HD;
+                const __nv_bfloat16* src = src0 + (long long)kvc.page(bt[lp]) * page_stride + (pos - lp * ps) * HD;
                 cp_async16(k_tile + dst[j], src);
                 cp_async16(v_tile + dst[j], src + v_off);
             }
@@ -243,11 +243,13 @@ attention_fa_kernel(const FaParams p) {
     if (DECODE && p.qkv != nullptr) {
         constexpr int HALF = HD / 2, QUADS = HD / 8;
         const int q_dim = p.heads * HD, kv_dim = p.kv.kv_heads * HD;
-        // new keys and values: by the one CTA whose tiles hold the new positions, into the cache
-        // (later steps read them there) before its own loads of those tiles are issued
-        if (p.write_kv && t_begin * FA_BN < kv_hi && kv_hi <= t_end * FA_BN) {
+        // new keys and values: each by the one CTA whose key tiles hold its position, into the
+        // cache (later steps read them there) before that CTA's own loads of those tiles are
+        // issued; no other CTA reads that tile
+        if (p.write_kv && t_begin < t_end && t_end * FA_BN > pos0) {
             for (int e = threadIdx.x; e < ntok * 2 * QUADS; e += FA_THREADS) {
                 const int j = e / (2 * QUADS), is_v = (e / QUADS) & 1, i0 = (e % QUADS) * 4;
+                if (pos0 + j < t_begin * FA_BN || pos0 + j >= t_end * FA_BN) continue;
                 float4 ra, rb;
                 rotated_quads(p, q_start + tok0 + j, q_dim + (is_v ? kv_dim : 0) + kvh * HD, HALF, i0, !is_v, ra, rb);
                 __nv_bfloat16* dst = p.pool_rw + p.kv.row(slot, pos0 + j, kvh) + (is_v ? p.kv.v_offset : 0);
@@ -458,74 +460,6 @@ attention_fa_kernel(const FaParams p) {
         mml[(warp * 16 + g + 8) * 2] = m_b; mml[(warp * 16 + g + 8) * 2 + 1] = l_b;
     }
     __syncthreads();
-    if (p.cluster) {
-        // The splits of this (item, kv head) are the CTAs of one cluster: each sends its merged
-        // partial to the first CTA's shared memory, which folds them in split order.  No
-        // scratch in global memory, no second kernel.
-        constexpr int EPT = 16 * HD / FA_THREADS;
-        float accv[EPT], mv[EPT], lv[EPT];
-#pragma unroll
-        for (int k = 0; k < EPT; ++k) {
-            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
-            float m = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
-            const float use = (m == -INFINITY) ? 0.f : m;
-            float l = 0.f, acc = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(mml[(w * 16 + r) * 2] - use);
-                l += mml[(w * 16 + r) * 2 + 1] * f;
-                acc += mo[(w * 16 + r) * HD + d] * f;
-            }
-            accv[k] = acc; mv[k] = m; lv[k] = l;
-        }
-        // every CTA of the cluster is done with its tiles and merge buffers: the first one's
-        // shared memory is free to receive
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        uint32_t lead;      // the first CTA's shared memory: [splits][16][HD] sums, then [splits][16][2] maxima and weights
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(lead) : "r"(smem), "r"(0));
-        const uint32_t lead_ml = lead + (uint32_t)p.n_splits * 16 * HD * 4;
-#pragma unroll
-        for (int k = 0; k < EPT; ++k) {
-            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
-            if (r >= rows_used) continue;
-            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead + (uint32_t)((split * 16 + r) * HD + d) * 4), "f"(accv[k]) : "memory");
-            if (d == 0) {
-                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead_ml + (uint32_t)((split * 16 + r) * 2) * 4), "f"(mv[k]) : "memory");
-                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lead_ml + (uint32_t)((split * 16 + r) * 2 + 1) * 4), "f"(lv[k]) : "memory");
-            }
-        }
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (split != 0) return;
-        float* red_o = reinterpret_cast<float*>(smem_raw);
-        float* red_ml = red_o + p.n_splits * 16 * HD;
-        if (threadIdx.x < rows_used) {
-            const int r = threadIdx.x;
-            float m = -INFINITY;
-            for (int s2 = 0; s2 < p.n_splits; ++s2) m = fmaxf(m, red_ml[(s2 * 16 + r) * 2]);
-            const float use = (m == -INFINITY) ? 0.f : m;
-            float l = 0.f;
-            for (int s2 = 0; s2 < p.n_splits; ++s2) {
-                const float f = exp2f(red_ml[(s2 * 16 + r) * 2] - use);
-                l += red_ml[(s2 * 16 + r) * 2 + 1] * f;
-                red_ml[(s2 * 16 + r) * 2] = f;
-            }
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            for (int s2 = 0; s2 < p.n_splits; ++s2) red_ml[(s2 * 16 + r) * 2] *= inv;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int k = 0; k < EPT; ++k) {
-            const int e = threadIdx.x + k * FA_THREADS, r = e / HD, d = e % HD;
-            if (r >= rows_used) continue;
-            float acc = 0.f;
-            for (int s2 = 0; s2 < p.n_splits; ++s2) acc += red_o[(s2 * 16 + r) * HD + d] * red_ml[(s2 * 16 + r) * 2];
-            const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
-            p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(acc);
-        }
-        return;
-    }
     for (int e = threadIdx.x; e < 16 * HD; e += FA_THREADS) {
         const int r = e / HD, d = e % HD;
         if (r >= rows_used) continue;
@@ -701,33 +635,8 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
     constexpr size_t tiles = (DECODE ? (size_t)BM * HD * 2 : 0) + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
     constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
     constexpr size_t smem = tiles > merge ? tiles : merge;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_fa_kernel<HD, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_error("axon_attention_fa: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; }
-        configured = true;
-    }
+    if (int st = ensure_dynamic_smem<attention_fa_kernel<HD, DECODE>>(smem, "axon_attention_fa")) return st;
     dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);
-    if (DECODE && p.cluster) {
-        // the splits of one (item, kv head) form a cluster (grid z)
-        static_assert(!DECODE || (size_t)8 * 16 * (HD + 2) * 4 <= smem, "the first CTA's shared memory takes every split's partial");
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(FA_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = 1;
-        attr[1].val.clusterDim.y = 1;
-        attr[1].val.clusterDim.z = (unsigned)p.n_splits;
-        cfg.attrs = attr;
-        cfg.numAttrs = 2;
-        cudaLaunchKernelEx(&cfg, attention_fa_kernel<HD, DECODE>, p);
-        return launch_status("axon_attention_fa");
-    }
     launch_pdl(attention_fa_kernel<HD, DECODE>, grid, dim3(FA_THREADS), smem, stream, p);
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
@@ -741,12 +650,6 @@ static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t 
 }  // namespace axon
 
 using namespace axon;
-
-struct AxonKvLayoutFa {
-    const int32_t* block_table;
-    int32_t table_stride, page_size, kv_heads, head_dim;
-    int64_t page_stride, entry_offset, v_offset;
-};
 
 // How many floats of scratch a decode launch with these sizes needs (0 when splits == 1).
 AXON_API long long axon_attention_fa_scratch_floats(int n_items, int kv_heads, int n_splits, int head_dim) {
@@ -769,7 +672,7 @@ struct FusedQkv {            // see FaParams::qkv
 }
 
 static int attention_fa_launch(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
-                               const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
+                               const int32_t* items, int n_items, const AxonKvLayout* layout, int heads,
                                float scale, int window, int decode, int tokens_per_tile, int n_splits,
                                float* scratch, unsigned int* counters, const FusedQkv& fused, cudaStream_t stream) {
     if (n_items <= 0) return AXON_OK;
@@ -778,9 +681,8 @@ static int attention_fa_launch(const void* q, const void* pool, void* out, const
     const int group = heads / kvh, bm = decode ? 16 : 64;
     if (tokens_per_tile < 1 || tokens_per_tile * group > bm) { set_error("axon_attention_fa: %d tokens x %d heads do not fit a tile of %d rows", tokens_per_tile, group, bm); return AXON_BAD_ARGUMENT; }
     if (n_splits < 1 || n_splits > FA_MAX_SPLITS || (!decode && n_splits != 1)) { set_error("axon_attention_fa: bad split count %d (1..%d; 1 for prefill tiles)", n_splits, FA_MAX_SPLITS); return AXON_BAD_ARGUMENT; }
-    // splits without scratch: the (at most 8) splits of an (item, kv head) run as one thread-block
-    // cluster and fold through the first CTA's shared memory
-    if (n_splits > 8 && scratch == nullptr) { set_error("axon_attention_fa: more than 8 splits need scratch memory"); return AXON_BAD_ARGUMENT; }
+    if (n_splits > 1 && scratch == nullptr) { set_error("axon_attention_fa: %d key splits need scratch memory for their partial results", n_splits); return AXON_BAD_ARGUMENT; }
+    if (layout->planes == 1 || (layout->v_dim > 0 && layout->v_dim != hd)) { set_error("axon_attention_fa: takes caches with key and value planes of one width"); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) { set_error("axon_attention_fa: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     FaParams p;
     p.q = (const __nv_bfloat16*)q; p.pool = (const __nv_bfloat16*)pool; p.out = (__nv_bfloat16*)out;
@@ -788,10 +690,7 @@ static int attention_fa_launch(const void* q, const void* pool, void* out, const
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (long long)n_items * kvh * n_splits * 16 * hd : nullptr;
     p.counters = (n_splits > 1 && scratch) ? counters : nullptr;
-    p.cluster = (decode && n_splits > 1 && scratch == nullptr) ? 1 : 0;
-    p.kv.block_table = layout->block_table; p.kv.table_stride = layout->table_stride; p.kv.page_size = layout->page_size;
-    p.kv.kv_heads = kvh; p.kv.head_dim = hd; p.kv.page_stride = layout->page_stride;
-    p.kv.entry_offset = layout->entry_offset; p.kv.v_offset = layout->v_offset;
+    p.kv = to_paged(layout);
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile;
     p.n_splits = n_splits; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -810,25 +709,28 @@ static int attention_fa_launch(const void* q, const void* pool, void* out, const
 }
 
 AXON_API int axon_attention_fa(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
-                               const int32_t* items, int n_items, const AxonKvLayoutFa* layout, int heads,
+                               const int32_t* items, int n_items, const AxonKvLayout* layout, int heads,
                                float scale, int window, int decode, int tokens_per_tile, int n_splits,
                                float* scratch, unsigned int* counters, cudaStream_t stream) {
     return attention_fa_launch(q, pool, out, segments, n_segments, items, n_items, layout, heads, scale, window, decode,
                                tokens_per_tile, n_splits, scratch, counters, FusedQkv{}, stream);
 }
 
-// Decode steps (every segment at most `tokens_per_tile` tokens, segment i is item i): rotation,
-// cache write and attention in one kernel.  qkv: float [tokens][(heads + 2 kv_heads) * hd] with
+// Decode steps (segment i is item i, and no segment holds more than `max_q_len` tokens, which
+// must not exceed `tokens_per_tile`: a longer segment would lose its further tokens, so the call
+// is refused): rotation, cache write and attention in one kernel.  Each new key and value is
+// written by the CTA whose share of the key tiles holds its position, before that CTA loads the tile.  qkv: float [tokens][(heads + 2 kv_heads) * hd] with
 // biases added, or (partial != null) still owed the partial sums of a deferred split-K product
 // with its bias.  table: (cos, sin) [tokens][hd / 2] for pairs (i, i + hd / 2) over the whole
 // head, or null for no rotation.  write_kv == 0: the cache holds the new positions already
 // (a layer reading another layer's cache).  Otherwise as axon_attention_fa with decode != 0.
 AXON_API int axon_attention_fa_decode_fused(const float* qkv, const float* partial, int fold_splits, int fold_ntok,
                                             const float* bias, const float* table, int write_kv, void* pool, void* out,
-                                            const int32_t* segments, int n_segments, const AxonKvLayoutFa* layout,
-                                            int heads, float scale, int window, int tokens_per_tile, int n_splits,
-                                            float* scratch, unsigned int* counters, cudaStream_t stream) {
+                                            const int32_t* segments, int n_segments, const AxonKvLayout* layout,
+                                            int heads, float scale, int window, int tokens_per_tile, int max_q_len,
+                                            int n_splits, float* scratch, unsigned int* counters, cudaStream_t stream) {
     const int hd = layout->head_dim;
+    if (max_q_len < 1 || max_q_len > tokens_per_tile) { set_error("axon_attention_fa_decode_fused: segments of up to %d tokens do not fit tiles of %d", max_q_len, tokens_per_tile); return AXON_BAD_ARGUMENT; }
     if (qkv == nullptr) { set_error("axon_attention_fa_decode_fused: no q/k/v product given"); return AXON_BAD_ARGUMENT; }
     if (hd % 8) { set_error("axon_attention_fa_decode_fused: head size %d is not a multiple of 8", hd); return AXON_BAD_ARGUMENT; }
     if (partial != nullptr && (fold_splits < 1 || fold_ntok < 1)) { set_error("axon_attention_fa_decode_fused: bad partial sums"); return AXON_BAD_ARGUMENT; }
@@ -862,7 +764,7 @@ unsigned int* g_fa_noalloc_counters_ptr[kMaxDevices] = {};
 
 int axon_attention_fa_decode_noalloc(const void* q, const void* pool, void* out, const int32_t* segments,
                                      int n_segments, const int32_t* items, int n_items,
-                                     const AxonKvLayoutFa* layout, int heads, float scale, int window,
+                                     const AxonKvLayout* layout, int heads, float scale, int window,
                                      int tokens_per_tile, int n_splits, cudaStream_t stream) {
     if (n_items <= 0) return AXON_OK;
     if (layout == nullptr || n_splits < 1) { set_error("axon_attention_fa_decode_noalloc: bad arguments"); return AXON_BAD_ARGUMENT; }

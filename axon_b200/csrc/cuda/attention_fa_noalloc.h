@@ -37,12 +37,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "kv_layout.h"   // struct AxonKvLayout, the cache description a caller fills in
+
 #define AXON_FA_NOALLOC_SCRATCH_FLOATS (4ll * 1024 * 1024)
 // arrival counters of the key splits, one per (item, kv head); launches with more items fold
 // their splits in a second kernel instead
 #define AXON_FA_NOALLOC_COUNTERS 4096
-
-struct AxonKvLayoutFa;
 
 #ifdef __cplusplus
 extern "C" {
@@ -52,7 +52,7 @@ extern "C" {
 __attribute__((visibility("default")))
 int axon_attention_fa_decode_noalloc(const void* q, const void* pool, void* out, const int32_t* segments,
                                      int n_segments, const int32_t* items, int n_items,
-                                     const struct AxonKvLayoutFa* layout, int heads, float scale, int window,
+                                     const struct AxonKvLayout* layout, int heads, float scale, int window,
                                      int tokens_per_tile, int n_splits, cudaStream_t stream);
 
 #ifdef __cplusplus

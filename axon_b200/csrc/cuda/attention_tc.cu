@@ -55,10 +55,10 @@ __device__ __forceinline__ void at_pages(int (&pg)[8], const AtRowMap& map, cons
     if (map.pages_per_tile) {
         const int first = (key0 / AT_BN) * map.pages_per_tile;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pg[j] = bt[min(first + map.page_of[j], map.last_page)];   // past the end: finite data, masked later
+        for (int j = 0; j < 8; ++j) pg[j] = kv.page(bt[min(first + map.page_of[j], map.last_page)]);   // past the end: finite data, masked later
     } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pg[j] = bt[min(key0 + (int)(threadIdx.x >> 4) + 8 * j, kv_len - 1) / kv.page_size];
+        for (int j = 0; j < 8; ++j) pg[j] = kv.page(bt[min(key0 + (int)(threadIdx.x >> 4) + 8 * j, kv_len - 1) / kv.page_size]);
     }
 }
 // One 64-key tile of K or V: two 8 KiB halves [dims 0..63 | 64..127][key][64 dims].  `src` points at
@@ -318,15 +318,9 @@ attention_tc_kernel(const AtParams p) {
 
 using namespace axon;
 
-struct AxonKvLayoutTc {
-    const int32_t* block_table;
-    int32_t table_stride, page_size, kv_heads, head_dim;
-    int64_t page_stride, entry_offset, v_offset;
-};
-
 // Prompt portions at head size 128: tiles of `tokens_per_tile` tokens x group heads (<= 128 rows).
 AXON_API int axon_attention_tc(const void* q, const void* pool, void* out, const int32_t* segments, int n_segments,
-                               const int32_t* items, int n_items, const AxonKvLayoutTc* layout, int heads, float scale,
+                               const int32_t* items, int n_items, const AxonKvLayout* layout, int heads, float scale,
                                int window, int tokens_per_tile, cudaStream_t stream) {
     if (n_items <= 0) return AXON_OK;
     const int kvh = layout->kv_heads;
@@ -339,18 +333,12 @@ AXON_API int axon_attention_tc(const void* q, const void* pool, void* out, const
     AtParams p;
     p.q = (const __nv_bfloat16*)q; p.pool = (const __nv_bfloat16*)pool; p.out = (__nv_bfloat16*)out;
     p.segments = segments; p.items = items;
-    p.kv.block_table = layout->block_table; p.kv.table_stride = layout->table_stride; p.kv.page_size = layout->page_size;
-    p.kv.kv_heads = kvh; p.kv.head_dim = AT_HD; p.kv.page_stride = layout->page_stride;
-    p.kv.entry_offset = layout->entry_offset; p.kv.v_offset = layout->v_offset;
+    if (layout->planes == 1 || (layout->v_dim > 0 && layout->v_dim != AT_HD)) { set_error("axon_attention_tc: takes caches with key and value planes of one width"); return AXON_BAD_ARGUMENT; }
+    p.kv = to_paged(layout);
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     constexpr size_t smem = 2 * AT_BM * 128 + 4 * (2 * AT_BN * 128) + AT_BM * 128 + 64;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_error("axon_attention_tc: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; }
-        configured = true;
-    }
+    if (int st = ensure_dynamic_smem<attention_tc_kernel>(smem, "axon_attention_tc")) return st;
     attention_tc_kernel<<<dim3(n_items, kvh), AT_THREADS, smem, stream>>>(p);
     return launch_status("axon_attention_tc");
 }

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "kv_layout.h"
 #include "pdl.cuh"
 
 #define AXON_API extern "C" __attribute__((visibility("default")))
@@ -117,7 +118,8 @@ struct SplitFold {
 
 // Where position `pos` of the request in `slot` lies: the element offset of row
 // (kv_head, pos % page_size) of its page within one layer's K (or V) plane.
-// Cache layout: pool[page][entry][2: K,V][kv_head][page_size][head_dim].
+// Cache layout: pool[page][entry][K plane | V plane], a plane being [kv_head][page_size][width]
+// with width head_dim for keys and v_dim for values (see kv_layout.h).
 struct PagedKv {
     const int32_t* block_table;  // [slots][table_stride]: logical page -> physical page
     int table_stride;
@@ -127,13 +129,66 @@ struct PagedKv {
     long long page_stride;   // elements between two pages of the pool
     long long entry_offset;  // elements from a page's start to this layer's K plane
     long long v_offset;      // elements from the K plane to the V plane
+    int v_dim;               // elements of a value row
+    int planes;              // 2, or 1 when values are read from the key plane
+    int n_pages;             // the sink page's index
+    uint32_t* fault;         // checked tables: see kv_layout.h
 
+    // A block-table entry as a kernel may follow it: itself, or with checked tables the sink
+    // page when it lies outside the pool (recorded in `fault`).
+    __device__ __forceinline__ int page(int entry) const {
+        if (fault != nullptr && (unsigned)entry > (unsigned)n_pages) {
+            fault[1] = (uint32_t)entry;
+            fault[0] = 1u;
+            return n_pages;
+        }
+        return entry;
+    }
     __device__ __forceinline__ long long row(int slot, int pos, int kv_head) const {
         const int lp = pos / page_size;
-        const int page = block_table[(long long)slot * table_stride + lp];
-        return (long long)page * page_stride + entry_offset +
+        const int pg = page(block_table[(long long)slot * table_stride + lp]);
+        return (long long)pg * page_stride + entry_offset +
                ((long long)kv_head * page_size + (pos - lp * page_size)) * head_dim;
     }
+    // the value row of the same position (from the pool's start, v_offset included)
+    __device__ __forceinline__ long long v_row(int slot, int pos, int kv_head) const {
+        const int lp = pos / page_size;
+        const int pg = page(block_table[(long long)slot * table_stride + lp]);
+        return (long long)pg * page_stride + entry_offset + v_offset +
+               ((long long)kv_head * page_size + (pos - lp * page_size)) * v_dim;
+    }
 };
+
+inline PagedKv to_paged(const AxonKvLayout* l) {
+    PagedKv k;
+    k.block_table = l->block_table;
+    k.table_stride = l->table_stride;
+    k.page_size = l->page_size;
+    k.kv_heads = l->kv_heads;
+    k.head_dim = l->head_dim;
+    k.page_stride = l->page_stride;
+    k.entry_offset = l->entry_offset;
+    k.v_offset = l->v_offset;
+    k.v_dim = l->v_dim > 0 ? l->v_dim : l->head_dim;
+    k.planes = l->planes == 1 ? 1 : 2;
+    k.n_pages = l->n_pages;
+    k.fault = l->fault;
+    return k;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize for a kernel, once per device (the attribute
+// belongs to the device's context, so a second GPU needs its own call).
+template <auto Kernel>
+inline int ensure_dynamic_smem(size_t bytes, const char* what) {
+    static bool done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("%s: no current device", what); return AXON_CUDA_ERROR; }
+    if (!done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) { set_error("%s: %s", what, cudaGetErrorString(e)); return AXON_CUDA_ERROR; }
+        done[dev] = true;
+    }
+    return AXON_OK;
+}
 
 }  // namespace axon

@@ -60,16 +60,20 @@ template <int BN, int STAGES, int EPI, int RM, bool TMA_OUT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out,
-               const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int ldo, int m_tiles) {
+               const float* __restrict__ bias, void* __restrict__ out, int M, int N, int K, int ldo, int m_tiles,
+               uint32_t stuck_wait_limit) {
+    // stuck_wait_limit != 0 (tests of the failure path only): the MMA thread never tells the
+    // epilogue that the accumulator is complete, and the epilogue's wait gives up after that many
+    // polls.  The kernel must then still end in order: error flag set, tensor memory freed.
     constexpr uint32_t A_BYTES = RM * TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr uint32_t TMEM_COLS = RM * BN <= 32 ? 32 : RM * BN <= 64 ? 64 : RM * BN <= 128 ? 128 : RM * BN <= 256 ? 256 : 512;
     extern __shared__ unsigned char smem_dyn[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
     __shared__ uint32_t tmem_slot;
     const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(&bars[0]);
-    const uint32_t empty0 = full0 + 8 * STAGES, tmem_full = full0 + 16 * STAGES;
+    const uint32_t empty0 = full0 + 8 * STAGES, tmem_full = full0 + 16 * STAGES, mma_done = tmem_full + 8;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x % m_tiles, n_tile = blockIdx.x / m_tiles;
@@ -79,6 +83,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tmem_full, 1);
+        mbar_init(mma_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // this warp owns tensor memory: RM * BN float columns for the accumulators
@@ -126,12 +131,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 umma_commit(empty0 + 8 * s);      // the stage is free once these MMAs have read it
             }
-            umma_commit(tmem_full);               // the accumulator is complete
+            if (stuck_wait_limit == 0) {
+                umma_commit(tmem_full);           // the accumulator is complete
+            } else {
+                // the failure test: the epilogue is never told; this thread still sees the MMAs
+                // through, so that nothing is in flight when tensor memory is freed
+                umma_commit(mma_done);
+                mbar_wait(mma_done, 0, 1);
+            }
         }
     } else {
         // ---- epilogue: warps 2..9; a warp reads tensor-memory lanes 32 * (warp % 4) .., and the
         // two warps of a lane quarter take every other 32-column chunk
-        mbar_wait(tmem_full, 0, 2);
+        mbar_wait(tmem_full, 0, 2, stuck_wait_limit ? stuck_wait_limit : TC_WAIT_LIMIT);
         __syncwarp();
         tc_fence_after();
         const int quarter = warp & 3, half = (warp - 2) >> 2;
@@ -603,20 +615,15 @@ static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtens
 
 template <int BN, int STAGES, int RM, bool TMA_OUT>
 static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const float* bias,
-                     void* out, int M, int N, int K, int ldo, cudaStream_t stream) {
+                     void* out, int M, int N, int K, int ldo, uint32_t stuck_wait_limit, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * (RM * TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     static_assert(smem >= 8 * 8192 + 1024, "the epilogue stages its chunks in the ring");
     const int m_tiles = (M + RM * TC_BM - 1) / (RM * TC_BM), n_tiles = (N + BN - 1) / BN;
     const dim3 grid((unsigned)(m_tiles * n_tiles)), block(TC_THREADS);
 #define AXON_TC_LAUNCH(E)                                                                                          \
     {                                                                                                              \
-        static bool configured = false;                                                                            \
-        if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) { set_error("axon_gemm_tc: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
-            configured = true;                                                                                     \
-        }                                                                                                          \
-        gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT><<<grid, block, smem, stream>>>(ma, mw, mo, bias, out, M, N, K, ldo, m_tiles); \
+        if (int st = ensure_dynamic_smem<gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT>>(smem, "axon_gemm_tc")) return st; \
+        gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT><<<grid, block, smem, stream>>>(ma, mw, mo, bias, out, M, N, K, ldo, m_tiles, stuck_wait_limit); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_TC_LAUNCH(TC_STORE_F32) break;
@@ -661,6 +668,7 @@ using namespace axon;
 // For tests and measurements: force the tile shape (rows 1 or 2 times 128; columns 128, 192,
 // 224 or 256); rm 0 gives the choice back to the model.
 static int g_force_rm = 0, g_force_bn = 0, g_force_plain_out = 0;
+static uint32_t g_stuck_wait_limit = 0;
 AXON_API void axon_gemm_tc_force_tile(int rm, int bn) { g_force_rm = rm; g_force_bn = bn; }
 // For tests: nonzero makes every output take the stores from registers, as outputs that TMA
 // cannot address do.
@@ -687,7 +695,7 @@ AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void*
     } else {
         mo = ma;
     }
-#define AXON_TC_ARGS epilogue, ma, mw, mo, bias, out, M, N, K, ldo, stream
+#define AXON_TC_ARGS epilogue, ma, mw, mo, bias, out, M, N, K, ldo, g_stuck_wait_limit, stream
 #define AXON_TC_SHAPE(BN, STAGES, RM) return tma_out ? launch_tc<BN, STAGES, RM, true>(AXON_TC_ARGS) : launch_tc<BN, STAGES, RM, false>(AXON_TC_ARGS)
     if (ts.rm == 2) {
         switch (ts.bn) {
@@ -717,12 +725,7 @@ static int launch_swap(int epi, const CUtensorMap& mw, const CUtensorMap& mx, co
     const dim3 grid((unsigned)(tiles * splits), (unsigned)((M + NTOK - 1) / NTOK)), block(192);
 #define AXON_SWAP_LAUNCH(E)                                                                                        \
     {                                                                                                              \
-        static bool configured = false;                                                                            \
-        if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<NTOK, STAGES, E, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) { set_error("axon_gemm_tc_small: %s", cudaGetErrorString(e)); return AXON_CUDA_ERROR; } \
-            configured = true;                                                                                     \
-        }                                                                                                          \
+        if (int st = ensure_dynamic_smem<gemm_tc_swap_kernel<NTOK, STAGES, E, R>>(smem, "axon_gemm_tc_small")) return st; \
         launch_pdl(gemm_tc_swap_kernel<NTOK, STAGES, E, R>, grid, block, smem, stream, mw, mx, bias, out, partial, counters, M, N, K, ldo, splits, per_split); \
     }
     switch (epi) {
@@ -791,6 +794,17 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     if (ntok == 128) return launch_swap<128, 5, 1>(AXON_SWAP_ARGS);
     return launch_swap<256, 4, 1>(AXON_SWAP_ARGS);
 #undef AXON_SWAP_ARGS
+}
+
+// For the test of the failure path: while `polls` != 0, axon_gemm_tc launches its kernel so that the
+// epilogue's wait for the accumulator is never answered and gives up after that many polls (the
+// output is then garbage and the status word reads 3).  0 restores normal launches.
+AXON_API void axon_gemm_tc_test_stuck_wait(unsigned int polls) { g_stuck_wait_limit = polls; }
+
+// Clears the status word (after a test of the failure path, or once a failure has been reported).
+AXON_API int axon_gemm_tc_clear_status() {
+    const unsigned int zero = 0;
+    return cudaMemcpyToSymbol(g_tc_error, &zero, sizeof zero) == cudaSuccess ? AXON_OK : AXON_CUDA_ERROR;
 }
 
 // 0 when no kernel of this file ever gave up on a wait; else 1 + the role (0 producer,

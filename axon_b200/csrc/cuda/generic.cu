@@ -233,11 +233,27 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
     pdl_wait();
     const int t = blockIdx.x;
     const int hd = kv.head_dim, half = hd / 2, rhalf = rot / 2;
-    const int q_dim = heads * hd, kv_dim = kv.kv_heads * hd;
-    const float* row = qkv + (long long)t * (q_dim + 2 * kv_dim);
+    // a row of the product: q heads and k heads of `hd`, then (two planes) v heads of `v_dim`
+    const int q_dim = heads * hd, k_dim = kv.kv_heads * hd;
+    const int vhalf = kv.planes == 2 ? kv.v_dim / 2 : 0;
+    const int width = q_dim + k_dim + kv.kv_heads * 2 * vhalf;
+    const float* row = qkv + (long long)t * width;
     const int pos = positions[t], slot = token_slot[t];
-    const int items = (heads + 2 * kv.kv_heads) * half;
+    const int qk_items = (heads + kv.kv_heads) * half;
+    const int items = qk_items + kv.kv_heads * vhalf;
     for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
+        if (it >= qk_items) {
+            // a pair of a value row: passed through as it is
+            if (!write_kv) continue;
+            const int kh = (it - qk_items) / vhalf, i = (it - qk_items) % vhalf;
+            const int col = q_dim + k_dim + kh * kv.v_dim + 2 * i;
+            const float a = fold.partial ? fold.at(t, col) : row[col];
+            const float b = fold.partial ? fold.at(t, col + 1) : row[col + 1];
+            T* dst = pool + kv.v_row(slot, pos, kh) + 2 * i;
+            stf(dst, a);
+            stf(dst + 1, b);
+            continue;
+        }
         const int h = it / half, i = it % half;
         // element indices of the pair this thread owns
         int ia, ib;
@@ -252,33 +268,18 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
             const int base = (table != nullptr) ? rot : 0;
             ia = base + 2 * j; ib = base + 2 * j + 1;
         }
-        if (h < heads) {
-            const float a = fold.partial ? fold.at(t, h * hd + ia) : row[h * hd + ia];
-            const float b = fold.partial ? fold.at(t, h * hd + ib) : row[h * hd + ib];
-            float ra = a, rb = b;
-            if (rotate) {
-                const float2 cs = table[(long long)t * rhalf + i];
-                ra = a * cs.x - b * cs.y;
-                rb = a * cs.y + b * cs.x;
-            }
-            stf(q_out + (long long)t * q_dim + h * hd + ia, ra);
-            stf(q_out + (long long)t * q_dim + h * hd + ib, rb);
-        } else if (write_kv) {
-            const bool is_v = h >= heads + kv.kv_heads;
-            const int kh = is_v ? h - heads - kv.kv_heads : h - heads;
-            const int col = q_dim + (is_v ? kv_dim : 0) + kh * hd;
-            const float a = fold.partial ? fold.at(t, col + ia) : row[col + ia];
-            const float b = fold.partial ? fold.at(t, col + ib) : row[col + ib];
-            float ra = a, rb = b;
-            if (rotate && !is_v) {
-                const float2 cs = table[(long long)t * rhalf + i];
-                ra = a * cs.x - b * cs.y;
-                rb = a * cs.y + b * cs.x;
-            }
-            T* dst = pool + kv.row(slot, pos, kh) + (is_v ? kv.v_offset : 0);
-            stf(dst + ia, ra);
-            stf(dst + ib, rb);
+        if (h >= heads && !write_kv) continue;
+        const float a = fold.partial ? fold.at(t, h * hd + ia) : row[h * hd + ia];
+        const float b = fold.partial ? fold.at(t, h * hd + ib) : row[h * hd + ib];
+        float ra = a, rb = b;
+        if (rotate) {
+            const float2 cs = table[(long long)t * rhalf + i];
+            ra = a * cs.x - b * cs.y;
+            rb = a * cs.y + b * cs.x;
         }
+        T* dst = h < heads ? q_out + (long long)t * q_dim + h * hd : pool + kv.row(slot, pos, h - heads);
+        stf(dst + ia, ra);
+        stf(dst + ib, rb);
     }
 }
 
@@ -335,7 +336,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
                        int window) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hd = kv.head_dim;
+    const int hd = kv.head_dim, vd = kv.v_dim;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (item >= (long long)n_tokens * heads) return;
     const int t = (int)(item / heads), h = (int)(item % heads);
@@ -369,11 +370,11 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
         const int cnt = min(32, pos - p0 + 1);
         for (int j = 0; j < cnt; ++j) {
             const float w = __shfl_sync(0xffffffffu, pj, j);
-            const T* vr = pool + kv.row(slot, p0 + j, kh) + kv.v_offset;
+            const T* vr = pool + kv.v_row(slot, p0 + j, kh);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(w, ldf(vr + d), acc[i]);
+                if (d < vd) acc[i] = fmaf(w, ldf(vr + d), acc[i]);
             }
         }
         m = m_new;
@@ -382,7 +383,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) stf(out + ((long long)t * heads + h) * hd + d, acc[i] * inv);
+        if (d < vd) stf(out + ((long long)t * heads + h) * vd + d, acc[i] * inv);
     }
 }
 
@@ -404,30 +405,6 @@ __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, 
 
 using namespace axon;
 
-// The layout record the host passes for paged caches (mirrors axon::PagedKv).
-struct AxonKvLayout {
-    const int32_t* block_table;
-    int32_t table_stride;
-    int32_t page_size;
-    int32_t kv_heads;
-    int32_t head_dim;
-    int64_t page_stride;
-    int64_t entry_offset;
-    int64_t v_offset;
-};
-
-static PagedKv to_paged(const AxonKvLayout* l) {
-    PagedKv k;
-    k.block_table = l->block_table;
-    k.table_stride = l->table_stride;
-    k.page_size = l->page_size;
-    k.kv_heads = l->kv_heads;
-    k.head_dim = l->head_dim;
-    k.page_stride = l->page_stride;
-    k.entry_offset = l->entry_offset;
-    k.v_offset = l->v_offset;
-    return k;
-}
 
 AXON_API const char* axon_last_error() { return g_error; }
 
@@ -584,7 +561,8 @@ AXON_API int axon_rope_kv_write(const float* qkv, const float* table, const int3
     const int hd = layout->head_dim;
     if (hd % 2 || rot % 2 || rot > hd || rot < 0) { set_error("axon_rope_kv_write: head size %d / rotated size %d must be even and rot <= head", hd, rot); return AXON_BAD_ARGUMENT; }
     PagedKv kv = to_paged(layout);
-    if (table != nullptr && !adjacent && rot == hd && hd % 8 == 0 &&
+    if (kv.planes == 2 && kv.v_dim % 2) { set_error("axon_rope_kv_write: value rows of %d elements are not even", kv.v_dim); return AXON_BAD_ARGUMENT; }
+    if (table != nullptr && !adjacent && rot == hd && hd % 8 == 0 && kv.planes == 2 && kv.v_dim == hd &&
         (((uintptr_t)qkv | (uintptr_t)table | (uintptr_t)q_out | (uintptr_t)pool | (uintptr_t)partial | (uintptr_t)bias) & 15) == 0 &&
         (layout->page_stride * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0 && (layout->entry_offset * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0 &&
         (layout->v_offset * (dtype == AXON_F32 ? 4 : 2)) % 16 == 0) {
@@ -597,7 +575,7 @@ AXON_API int axon_rope_kv_write(const float* qkv, const float* table, const int3
         else { set_error("axon_rope_kv_write: unknown dtype %d", dtype); return AXON_BAD_ARGUMENT; }
         return launch_status("axon_rope_kv_write");
     }
-    const int items = (heads + 2 * layout->kv_heads) * (hd / 2);
+    const int items = (heads + layout->kv_heads) * (hd / 2) + (kv.planes == 2 ? layout->kv_heads * (kv.v_dim / 2) : 0);
     dim3 grid(n, (items + 255) / 256 > 8 ? 8 : (items + 255) / 256);
     if (dtype == AXON_F32)
         launch_pdl(rope_kv_write_kernel<float>, grid, dim3(256), 0, stream, qkv, (const float2*)table, positions, token_slot, (float*)q_out, (float*)pool, kv, heads, rot, adjacent, write_kv, fold);
@@ -613,6 +591,7 @@ AXON_API int axon_attention_plain(const void* q, const void* pool, int dtype, co
     if (n <= 0) return AXON_OK;
     const int hd = layout->head_dim;
     if (hd > 256 || hd < 1) { set_error("axon_attention_plain: head size %d is not in 1..256", hd); return AXON_BAD_ARGUMENT; }
+    if (layout->v_dim > 256) { set_error("axon_attention_plain: value rows of %d elements exceed 256", layout->v_dim); return AXON_BAD_ARGUMENT; }
     if (heads % layout->kv_heads) { set_error("axon_attention_plain: %d heads over %d kv heads", heads, layout->kv_heads); return AXON_BAD_ARGUMENT; }
     const int warps = 4;
     const long long items = (long long)n * heads;

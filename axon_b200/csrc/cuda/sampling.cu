@@ -99,12 +99,12 @@ __device__ __forceinline__ int digit_of_rank(const unsigned int* hist, int& rem)
 
 // best[r] = the id of the largest logit of row r (last index among equal maxima;
 // a NaN is picked only when the whole row is NaN, then the last index).
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ best, int vocab,
-                              long long row_stride) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, const int32_t* __restrict__ row_index,
+                              int32_t* __restrict__ best, int vocab, long long row_stride) {
     __shared__ unsigned long long sm[32];
     pdl_launch_dependents();
     pdl_wait();
-    const float* row = logits + (long long)blockIdx.x * row_stride;
+    const float* row = logits + (long long)(row_index ? row_index[blockIdx.x] : blockIdx.x) * row_stride;
     unsigned long long k = 0;
     int tail = 0;
     if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
@@ -200,7 +200,7 @@ __device__ void topk_select_general(const float* __restrict__ row, int vocab, in
 // largest lies; the second pass takes everything above that byte and pools the values of that
 // byte in shared memory, where seven more passes over the few pooled keys settle the rest.
 __global__ void __launch_bounds__(1024)
-topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
+topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ row_index, const int32_t* __restrict__ ks,
             float* __restrict__ cand_logit, int32_t* __restrict__ cand_id, int vocab,
             long long row_stride) {
     extern __shared__ __align__(16) unsigned char topk_smem[];   // 32 KiB: per-warp histograms, then the pool
@@ -211,7 +211,7 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     __shared__ int remaining_s, n_picked, n_pool;
     __shared__ unsigned long long picked[CAND_MAX];
     const int r = blockIdx.x, warp = threadIdx.x >> 5;
-    const float* row = logits + (long long)r * row_stride;
+    const float* row = logits + (long long)(row_index ? row_index[r] : r) * row_stride;
     int k = ks[r];
     if (k > vocab) k = vocab;
     if (k > CAND_MAX) k = CAND_MAX;
@@ -302,7 +302,8 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
 // weight exp((l - max) / T) first passes u * total, ids ascending.  Sums are in
 // double; each thread owns one contiguous stretch of the row.
 __global__ void __launch_bounds__(1024)
-sample_temperature_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+sample_temperature_kernel(const float* __restrict__ logits, const int32_t* __restrict__ row_index,
+                          const float* __restrict__ temperature,
                           const double* __restrict__ uniform, int32_t* __restrict__ picked, int vocab,
                           long long row_stride) {
     __shared__ float redf[32];
@@ -310,7 +311,7 @@ sample_temperature_kernel(const float* __restrict__ logits, const float* __restr
     __shared__ double total_s;
     __shared__ int chosen;
     const int r = blockIdx.x;
-    const float* row = logits + (long long)r * row_stride;
+    const float* row = logits + (long long)(row_index ? row_index[r] : r) * row_stride;
     const float inv_t = 1.0f / temperature[r];
     float m = -INFINITY;
     for_each_logit(row, vocab, [&](float v, int) { if (v == v) m = fmaxf(m, v); });
@@ -381,15 +382,42 @@ sample_temperature_kernel(const float* __restrict__ logits, const float* __restr
     }
 }
 
+// dst[r] = src[row_index[r]] (whole rows of floats): the copy that the penalty may write into.
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int32_t* __restrict__ row_index,
+                                   float* __restrict__ dst, int width, long long src_stride) {
+    const float* from = src + (long long)(row_index ? row_index[blockIdx.y] : blockIdx.y) * src_stride;
+    float* to = dst + (long long)blockIdx.y * width;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) to[i] = from[i];
+}
+
 }  // namespace axon
 
 using namespace axon;
+
+// dst [rows][width] contiguous; row_index (may be null: rows in order) picks the rows of src.
+AXON_API int axon_gather_rows(const float* src, const int32_t* row_index, float* dst, int rows, int width,
+                              long long src_stride, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return AXON_OK;
+    const int bx = (width + 1023) / 1024 > 64 ? 64 : (width + 1023) / 1024;
+    gather_rows_kernel<<<dim3(bx, rows), 256, 0, stream>>>(src, row_index, dst, width, src_stride);
+    return launch_status("axon_gather_rows");
+}
+
+// In the three pickers below `row_index` (may be null) names the row of `logits` that output row r
+// reads, so that a caller picks from some rows of a batch without copying them.
+AXON_API int axon_argmax_rows(const float* logits, const int32_t* row_index, int32_t* best, int rows, int vocab,
+                              long long row_stride, cudaStream_t stream) {
+    if (rows <= 0) return AXON_OK;
+    if (vocab <= 0) { set_error("axon_argmax: empty rows"); return AXON_BAD_ARGUMENT; }
+    launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, row_index, best, vocab, row_stride);
+    return launch_status("axon_argmax");
+}
 
 AXON_API int axon_argmax(const float* logits, int32_t* best, int rows, int vocab, long long row_stride,
                          cudaStream_t stream) {
     if (rows <= 0) return AXON_OK;
     if (vocab <= 0) { set_error("axon_argmax: empty rows"); return AXON_BAD_ARGUMENT; }
-    launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, best, vocab, row_stride);
+    launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, (const int32_t*)nullptr, best, vocab, row_stride);
     return launch_status("axon_argmax");
 }
 
@@ -403,19 +431,19 @@ AXON_API int axon_repeat_penalty(float* logits, const int32_t* ids, const float*
 AXON_API int axon_topk_max() { return CAND_MAX; }
 
 // cand_logit / cand_id: [rows][256]; ks[r] <= 256 entries of row r are written.
-AXON_API int axon_topk(const float* logits, const int32_t* ks, float* cand_logit, int32_t* cand_id,
+AXON_API int axon_topk(const float* logits, const int32_t* row_index, const int32_t* ks, float* cand_logit, int32_t* cand_id,
                        int rows, int vocab, long long row_stride, cudaStream_t stream) {
     if (rows <= 0) return AXON_OK;
     if (vocab <= 0) { set_error("axon_topk: empty rows"); return AXON_BAD_ARGUMENT; }
-    topk_kernel<<<rows, 1024, 32 * 1024, stream>>>(logits, ks, cand_logit, cand_id, vocab, row_stride);
+    topk_kernel<<<rows, 1024, 32 * 1024, stream>>>(logits, row_index, ks, cand_logit, cand_id, vocab, row_stride);
     return launch_status("axon_topk");
 }
 
-AXON_API int axon_sample_temperature(const float* logits, const float* temperature,
+AXON_API int axon_sample_temperature(const float* logits, const int32_t* row_index, const float* temperature,
                                      const double* uniform, int32_t* picked, int rows, int vocab,
                                      long long row_stride, cudaStream_t stream) {
     if (rows <= 0) return AXON_OK;
     if (vocab <= 0) { set_error("axon_sample_temperature: empty rows"); return AXON_BAD_ARGUMENT; }
-    sample_temperature_kernel<<<rows, 1024, 0, stream>>>(logits, temperature, uniform, picked, vocab, row_stride);
+    sample_temperature_kernel<<<rows, 1024, 0, stream>>>(logits, row_index, temperature, uniform, picked, vocab, row_stride);
     return launch_status("axon_sample_temperature");
 }

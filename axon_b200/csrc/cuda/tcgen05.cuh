@@ -26,9 +26,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Wait until the phase with this parity completes, at most TC_WAIT_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t role) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+// Wait until the phase with this parity completes, at most `limit` polls.  A wait that gives up
+// records 1 + its role in the error flag and returns false; the caller carries on to its end.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t role, uint32_t limit = TC_WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");

@@ -48,13 +48,12 @@ class DecoderModel:
         self.blocks = [build("block", PartSpec(l.block, l.params, {}, l.parts)) for l in spec.layers]
         self.final_norm = build("norm", spec.final_norm)
         self.head = build("head", spec.head)
-        #: what each schedule entry keeps in the cache (None when it keeps nothing of its own)
-        self.needs: List[Union[KvNeed, StateNeed, None]] = []
+        #: what each schedule entry keeps in the cache: {part path: need} over the cache-keeping
+        #: parts of its layer (empty when it keeps nothing of its own)
+        self.needs: List[Dict[str, Union[KvNeed, StateNeed]]] = []
+        per_layer = [layer_cache_needs(l) for l in spec.layers]
         for e in spec.schedule:
-            layer = spec.layers[e.layer]
-            mixer = layer.parts.get("mixer")
-            need = part_class("mixer", mixer.kind).cache_need(mixer) if mixer is not None else None
-            self.needs.append(None if e.cache_of is not None else need)
+            self.needs.append({} if e.cache_of is not None else dict(per_layer[e.layer]))
 
     def cache_owner(self, entry: int) -> int:
         e = self.spec.schedule[entry]
@@ -109,6 +108,26 @@ class DecoderModel:
             logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         self.head.forward(h, logits)
         return logits
+
+
+def layer_cache_needs(layer) -> Dict[str, Union[KvNeed, StateNeed]]:
+    """What a layer keeps in the cache: ``{part path: need}`` for every part of its arrangement,
+    nested ones included (paths are dotted: ``"mixer"``, ``"mixer.inner"``), whose class
+    answers ``cache_need`` with something.  A layer may hold several such parts (attention
+    beside a mixer with state, say) or none; no part name is special."""
+    out: Dict[str, Union[KvNeed, StateNeed]] = {}
+
+    def rec(category: str, ps: PartSpec, path: str) -> None:
+        cls = part_class(category, ps.kind)
+        need = cls.cache_need(ps)
+        if need is not None:
+            out[path or ps.kind] = need
+        nested = getattr(cls, "nested", {})
+        for name, sub in ps.parts.items():
+            rec(nested.get(name, name), sub, f"{path}.{name}" if path else name)
+
+    rec("block", PartSpec(layer.block, layer.params, {}, layer.parts), "")
+    return out
 
 
 def _shape_of(spec: PartSpec):

@@ -63,6 +63,8 @@ class BatchRunner:
             for rid, tok in picked.items():
                 if not (rid in done_ids and done_ids[rid] == lib.host().Finish.Stop):
                     on_token(rid, tok)
+        if done:
+            self.engine.check_device()      # before a request's tokens are handed out as good
         for d in done:
             self.outputs[d.id] = list(self.sched.take_output(d.id))
             self.finish[d.id] = d.finish.name

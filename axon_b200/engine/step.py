@@ -35,6 +35,13 @@ class OutOfPages(StepError):
     """A request's next tokens need more pages than are free."""
 
 
+class DeviceFault(RuntimeError):
+    """A kernel reported that it could not do its work (a bounded wait inside it gave up, or
+    with checked tables a block-table entry lay outside the pool).  What the step returned
+    is not to be trusted; the reference treats a device error as fatal too
+    (``StepError::Device``, src/lm.rs:262-270)."""
+
+
 @dataclass
 class StepEntry:
     slot: int
@@ -216,15 +223,20 @@ class Engine:
                                 seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len)
             graph_key = (n, n_want, self.model.graph_key(probe), bool(greedy))
         elif self.cuda_graphs and self.prefill_graphs and s == 1 and n > 1:
-            # one request's portion: nothing the host works out for it depends on where in the
-            # request it lies (positions, lengths and tables are read from device memory)
-            key = ("portion", n, n_want, bool(greedy))
+            # one request's portion: what the host works out for it does not depend on where in
+            # the request it lies (positions, lengths and tables are read from device memory),
+            # except what the parts report in their keys (a portion short enough for the
+            # attention's decode shape takes its split count from the context's length)
+            probe = StepContext(rt=self.rt, n_tokens=n, tokens=None, positions=None, token_slot=None,
+                                seg_slot=seg_slot, seg_q_start=seg_q_start, seg_q_len=seg_q_len, seg_kv_len=seg_kv_len)
+            key = ("portion", n, n_want, self.model.graph_key(probe), bool(greedy))
             seen = self._shape_seen.get(key, 0) + 1
             if len(self._shape_seen) > 4096:
                 self._shape_seen.clear()
             self._shape_seen[key] = seen
             if seen >= 2:
                 graph_key = key
+        # (a graph holds the address of the metadata it was captured with: one buffer per kind and shape)
         meta_name = "step_meta" if graph_key is None else f"step_meta_graph_{'p' if graph_key[0] == 'portion' else 'd'}_{n}_{n_want}"
         dev = self.rt.buffer(meta_name, (total,), torch.int32)
         dev.copy_(stage[:total], non_blocking=True)
@@ -257,7 +269,24 @@ class Engine:
             for e, start in zip(entries, starts):
                 cache.commit(e.slot, start + len(e.tokens))
         self.steps += 1
+        if cache.checks_tables:
+            bad = cache.fault()
+            if bad is not None:
+                raise DeviceFault(f"a kernel met block-table entry {bad}, outside the pool of {cache.n_pages} pages "
+                                  "(it used the sink page instead; the step's results are void)")
         return logits
+
+    def check_device(self) -> None:
+        """Raise :class:`DeviceFault` if a bounded wait inside a tensor-core kernel ever gave up.
+        Synchronises the device, so callers ask where they wait for results anyway (at a
+        request's end, every so many steps)."""
+        if self.rt.precise:
+            return
+        from ..kernels import fast
+        for what, status in (("product", fast.gemm_tc_status()), ("attention", fast.attention_tc_status())):
+            if status:
+                raise DeviceFault(f"a tensor-core {what} kernel gave up waiting (status {status}: 1 + the role that "
+                                  "waited: 0 loads, 1 MMA, 2 epilogue; 100: misaligned shared memory)")
 
     def _graph_step(self, key, context, want_rows, n_want, greedy: bool = False) -> Optional[torch.Tensor]:
         """Run a decode-only step through its CUDA graph, capturing it the first time.

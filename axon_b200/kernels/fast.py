@@ -8,7 +8,6 @@ checked here, before the launch, so a refusal never costs a failed launch.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -22,7 +21,7 @@ EPI_STORE_F32, EPI_STORE_BF16, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 #: of the other kernel would leave most SMs without one (measured at 7B sizes, 128 rows: down
 #: projection 57 us against 102 us; gate/up, 148 tiles, 96 us against 63 us).
 SMALL_M = 64
-SWAP_MAX_ROWS = int(os.environ.get("AXON_SWAP_MAX_ROWS", 1024))
+SWAP_MAX_ROWS = 1024
 
 
 def _takes_swapped_kernel(M: int, N: int) -> bool:
@@ -31,9 +30,8 @@ def _takes_swapped_kernel(M: int, N: int) -> bool:
     return M <= SWAP_MAX_ROWS and -(-M // 256) * -(-N // 256) < 100
 
 #: switches for tests that compare a tuned kernel with the plain one
-ENABLED = {"gemm_tc_small": True, "gemm_small_m": True, "gemm_tc": True, "attention_prefill": True,
-           "attention_decode": True, "attention_tc": True,
-           "attention_fused": os.environ.get("AXON_FA_FUSED", "1") != "0"}
+ENABLED = {"gemm_tc_small": True, "gemm_tc": True, "attention_prefill": True,
+           "attention_decode": True, "attention_tc": True, "attention_fused": True}
 
 
 _stream = lib.current_stream
@@ -42,10 +40,7 @@ _stream = lib.current_stream
 _SPLIT_SCRATCH = {}
 #: how many CTAs a product for few rows aims at (K is cut into slabs until there are about
 #: this many): one per SM measured best, because the CTAs of the next kernel then fit beside them and preload their weights
-SPLIT_TARGET_CTAS = int(os.environ.get("AXON_SPLIT_TARGET_CTAS", 148))
-#: experiments: products with at most this many weight rows and at most 8 tokens take the
-#: mma.sync kernel instead of the swapped tcgen05 one (0 = never)
-MMA_SYNC_MAX_ROWS = int(os.environ.get("AXON_MMA_SYNC_MAX_ROWS", 0))
+SPLIT_TARGET_CTAS = 148
 
 
 def _split_scratch(device: torch.device):
@@ -92,14 +87,14 @@ def forget_owed(device: torch.device) -> None:
             _OUTSTANDING[k] = None
 
 #: whether products for few rows may leave their partial sums to the reader of the output
-DEFER_FOLD = os.environ.get("AXON_DEFER_FOLD", "1") != "0"
+#: (tests switch it off to compare the two ways of folding)
+DEFER_FOLD = True
 
 
 def _gemm_small(a, w, bias, out, epi, M, N, K, defer: bool = False):
-    """Few rows (``_takes_swapped_kernel``): the swapped tcgen05 kernel, or for at most 64 rows the
-    mma.sync one when that is switched off.  With ``defer`` a
+    """Few rows (``_takes_swapped_kernel``): the swapped tcgen05 kernel.  With ``defer`` a
     split product returns a PendingFold instead of folding its partial sums itself."""
-    if ENABLED["gemm_tc_small"] and not (M <= 8 and N <= MMA_SYNC_MAX_ROWS):
+    if ENABLED["gemm_tc_small"]:
         partial, counters, _ = _split_scratch(a.device)
         owed = _OUTSTANDING.get(a.device)
         if owed is not None and not owed.claimed:
@@ -114,10 +109,6 @@ def _gemm_small(a, w, bias, out, epi, M, N, K, defer: bool = False):
             owed = PendingFold(partial, plan[0], plan[1], bias, out, epi == EPI_RESIDUAL)
             _OUTSTANDING[a.device] = owed
             return owed
-        return True
-    if ENABLED["gemm_small_m"] and M <= SMALL_M:
-        check(lib.cuda().axon_gemm_small_m(a.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
-                                           out.data_ptr(), epi, M, N, K, K, out.stride(0), _stream()))
         return True
     return False
 
@@ -185,21 +176,18 @@ FA_MAX_SPLITS = 32
 #: CTAs the decode attention never exceeds when it splits the keys of each request: two CTAs fit
 #: an SM, and a launch that spills into a second wave pays for it (measured at 7B sizes: 320 CTAs
 #: at batch 16 cost 10 % of the step against 256)
-FA_TARGET_CTAS = int(os.environ.get("AXON_FA_TARGET_CTAS", 2 * 148))
+FA_TARGET_CTAS = 2 * 148
 #: the split rule's model, in units of one key tile's time in a CTA: what each further share adds to
 #: the fold, and what the fold's kernel costs when there is one
-FA_SPLIT_COST = float(os.environ.get("AXON_FA_SPLIT_COST", 0.15))
-FA_FOLD_COST = float(os.environ.get("AXON_FA_FOLD_COST", 2.0))
+FA_SPLIT_COST = 0.15
+FA_FOLD_COST = 2.0
 #: launches of more CTAs than this pay a further tile's time in the model
 FA_ROOMY_CTAS, FA_CROWD_COST = 256, 1.0
 #: whether the last split folds the partials itself (else a second kernel does; measured at 7B
 #: sizes the second kernel is a little faster up to batch 8 and equal at 64, because it overlaps
 #: with the kernels around it while the in-kernel fold lengthens the slowest CTA)
-FA_FOLD_IN_KERNEL = os.environ.get("AXON_FA_FOLD_IN_KERNEL", "0") != "0"
-#: whether few splits fold through a thread-block cluster's shared memory instead of scratch and a
-#: second kernel.  Off: measured at 7B sizes and batch 8 the step is 6 % slower with it, because a
-#: cluster of 8 CTAs waits until 8 SMs of one GPC have room at once, beside the products' CTAs.
-FA_CLUSTER = os.environ.get("AXON_FA_CLUSTER", "0") != "0"
+#: (the entry point that allocates nothing folds this way; tests switch it on to cover it)
+FA_FOLD_IN_KERNEL = False
 SM_COUNT = 148
 
 
@@ -267,14 +255,10 @@ def decode_split_count(n_dec: int, kv_heads: int, max_kv_len: int) -> int:
 
 
 def _decode_splits(n_dec: int, kv, tiles: int, rt):
-    """Key splits for the decode shape and the scratch their partials go to (None: a cluster folds)."""
+    """Key splits for the decode shape and the scratch their partials go to (None: one split)."""
     splits = _key_splits(n_dec * kv.kv_heads, tiles)
     scratch = None
-    # up to 8 splits of at most 16 tiles each fold inside a thread-block cluster (no scratch,
-    # no second kernel); longer contexts keep more, independent splits
-    if FA_CLUSTER and splits > 1 and -(-tiles // min(splits, 8)) <= 16:
-        splits = min(splits, 8)
-    elif splits > 1:
+    if splits > 1:
         # sized for the most splits this batch can get, so that the buffer never moves
         # while the contexts grow (captured graphs hold its address)
         most = max(1, min(FA_MAX_SPLITS, FA_TARGET_CTAS // (n_dec * kv.kv_heads)))
@@ -291,6 +275,8 @@ def attention_decode_fused(qkv, pending, table, rot: int, adjacent: bool, kv, ct
     if not (ENABLED["attention_decode"] and ENABLED["attention_fused"]) or ctx.unit_items is None:
         return False
     if out.dtype != torch.bfloat16 or kv.pool.dtype != torch.bfloat16 or kv.head_dim not in FA_HEAD_DIMS:
+        return False
+    if kv.planes != 2 or kv.v_dim != kv.head_dim:
         return False
     if heads % kv.kv_heads or heads // kv.kv_heads > 16 or ctx.segments is None or qkv.dtype != torch.float32:
         return False
@@ -313,7 +299,8 @@ def attention_decode_fused(qkv, pending, table, rot: int, adjacent: bool, kv, ct
         0 if pending is None else pending.splits, 0 if pending is None else pending.ntok,
         None if pending is None or pending.bias is None else pending.bias.data_ptr(),
         None if table is None else table.data_ptr(), int(write_kv), kv.pool.data_ptr(), out.data_ptr(),
-        ctx.segments.data_ptr(), n, kv._ref, heads, float(scale), int(kv.window), 16 // (heads // kv.kv_heads), splits,
+        ctx.segments.data_ptr(), n, kv._ref, heads, float(scale), int(kv.window), 16 // (heads // kv.kv_heads),
+        ctx.max_q_len, splits,
         None if scratch is None else scratch.data_ptr(),
         counters.data_ptr() if FA_FOLD_IN_KERNEL and n * kv.kv_heads <= counters.numel() else None, _stream()))
     return True
@@ -325,6 +312,8 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     if not (ENABLED["attention_prefill"] and ENABLED["attention_decode"]):
         return False
     if q.dtype != torch.bfloat16 or kv.pool.dtype != torch.bfloat16 or kv.head_dim not in FA_HEAD_DIMS:
+        return False
+    if kv.planes != 2 or kv.v_dim != kv.head_dim:
         return False
     if heads % kv.kv_heads or heads // kv.kv_heads > 64 or ctx.segments is None:
         return False

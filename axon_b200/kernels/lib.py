@@ -34,6 +34,11 @@ class KvLayout(ctypes.Structure):
         ("page_stride", c_int64),
         ("entry_offset", c_int64),
         ("v_offset", c_int64),
+        ("v_dim", ctypes.c_int32),
+        ("planes", ctypes.c_int32),
+        ("n_pages", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("fault", c_void_p),
     ]
 
 
@@ -53,17 +58,19 @@ _SIGNATURES = {
     "axon_convert": [P, c_int, P, c_int, c_longlong, P],
     "axon_argmax": [P, P, c_int, c_int, c_longlong, P],
     "axon_repeat_penalty": [P, P, P, c_int, c_int, c_longlong, c_int, P],
-    "axon_topk": [P, P, P, P, c_int, c_int, c_longlong, P],
-    "axon_sample_temperature": [P, P, P, P, c_int, c_int, c_longlong, P],
-    "axon_gemm_small_m": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "axon_argmax_rows": [P, P, P, c_int, c_int, c_longlong, P],
+    "axon_gather_rows": [P, P, P, c_int, c_int, c_longlong, P],
+    "axon_topk": [P, P, P, P, P, c_int, c_int, c_longlong, P],
+    "axon_sample_temperature": [P, P, P, P, P, c_int, c_int, c_longlong, P],
     "axon_gemm_tc": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "axon_gemm_tc_status": [],
+    "axon_gemm_tc_clear_status": [],
     "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, c_int,
                            ctypes.POINTER(c_int), P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
     "axon_attention_fa_decode_fused": [P, P, c_int, c_int, P, P, c_int, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int,
-                                       c_float, c_int, c_int, c_int, P, P, P],
+                                       c_float, c_int, c_int, c_int, c_int, P, P, P],
     "axon_attention_tc": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int, P],
     "axon_attention_tc_status": [],
 }
@@ -106,6 +113,8 @@ def cuda() -> ctypes.CDLL:
         lib.axon_gemm_tc_force_tile.argtypes = [c_int, c_int]
         lib.axon_gemm_tc_force_plain_out.restype = None
         lib.axon_gemm_tc_force_plain_out.argtypes = [c_int]
+        lib.axon_gemm_tc_test_stuck_wait.restype = None
+        lib.axon_gemm_tc_test_stuck_wait.argtypes = [ctypes.c_uint]
         for name, sig in list(_SIGNATURES.items()) + list(_OPTIONAL_SIGNATURES.items()):
             try:
                 _declare(lib, name, sig)

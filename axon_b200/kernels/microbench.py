@@ -89,7 +89,7 @@ def main() -> int:
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--target-ctas", type=int, default=0, help="gemm_small_m: CTAs the split-K aims at")
     ap.add_argument("--tile", default="", help="gemm_tc: force the tile shape, e.g. 2x256 (rows/128 x columns)")
-    ap.add_argument("--mma-sync", action="store_true", help="gemm_small_m, attention_prefill: the mma.sync kernel, not the tcgen05 one")
+    ap.add_argument("--mma-sync", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         print("microbench needs a CUDA GPU", file=sys.stderr)
@@ -110,14 +110,12 @@ def main() -> int:
         if a.kernel == "gemm_small_m":
             fast.SMALL_M = fast.SWAP_MAX_ROWS = 1024                               # the swapped kernel at any size it takes
         if a.kernel == "gemm_tc":
-            fast.ENABLED["gemm_small_m"] = fast.ENABLED["gemm_tc_small"] = False   # the 128-row-tile kernel
+            fast.ENABLED["gemm_tc_small"] = False                                   # the 128-row-tile kernel
         if a.tile:
             rm, bn = a.tile.split("x")
             lib.cuda().axon_gemm_tc_force_tile(int(rm), int(bn))
         if a.target_ctas:
             fast.SPLIT_TARGET_CTAS = a.target_ctas
-        if a.mma_sync:
-            fast.ENABLED["gemm_tc_small"] = False                                   # the mma.sync kernel
         us, best = _time(fn, a.iters, a.warmup, flush)
         nbytes = 2 * (a.n * a.k + a.m * a.k) + out.numel() * out.element_size()
         _report(a.kernel, a, us, best, nbytes, 2 * a.m * a.n * a.k)

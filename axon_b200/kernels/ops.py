@@ -47,8 +47,12 @@ class KvView:
     """One schedule entry's keys and values inside its group's page pool.
 
     ``pool`` is ``[pages + 1][entries][2][kv_heads][page_size][head_dim]`` (the last
-    page is the sink); ``block_table`` is the group's device table
-    ``[slots][stride]`` of int32.
+    page is the sink) when keys and values are alike, else ``[pages + 1][entries][elements]``
+    with an entry's key plane ``[kv_heads][page_size][head_dim]`` followed, when ``planes``
+    is 2, by its value plane ``[kv_heads][page_size][v_dim]``.  With one plane the kernels
+    read values from the key plane.  ``block_table`` is the group's device table
+    ``[slots][stride]`` of int32.  ``fault`` (two uint32 on the device) switches checked
+    tables on: see ``kv_layout.h``.
     """
 
     pool: torch.Tensor
@@ -58,15 +62,41 @@ class KvView:
     kv_heads: int
     head_dim: int
     window: int = 0
+    v_dim: int = 0
+    planes: int = 2
+    fault: Optional[torch.Tensor] = None
 
     def __post_init__(self) -> None:
+        if self.planes not in (1, 2):
+            raise ValueError(f"a cache entry has one or two planes, not {self.planes}")
+        self.v_dim = self.head_dim if self.planes == 1 or not self.v_dim else self.v_dim
         entries = self.pool.shape[1]
-        plane = self.kv_heads * self.page_size * self.head_dim
+        self.k_plane = self.kv_heads * self.page_size * self.head_dim
+        self.v_plane = self.kv_heads * self.page_size * self.v_dim if self.planes == 2 else 0
+        per_entry = self.k_plane + self.v_plane
+        if self.pool[0].numel() != entries * per_entry:
+            raise ValueError(f"a page of {self.pool[0].numel()} elements does not hold {entries} entries of {per_entry}")
+        self.n_pages = self.pool.shape[0] - 1
         self.layout = KvLayout(
             block_table=self.block_table.data_ptr(), table_stride=self.block_table.shape[1],
             page_size=self.page_size, kv_heads=self.kv_heads, head_dim=self.head_dim,
-            page_stride=entries * 2 * plane, entry_offset=self.entry * 2 * plane, v_offset=plane)
+            page_stride=entries * per_entry, entry_offset=self.entry * per_entry,
+            v_offset=self.k_plane if self.planes == 2 else 0, v_dim=self.v_dim, planes=self.planes,
+            n_pages=self.n_pages, reserved=0, fault=None if self.fault is None else self.fault.data_ptr())
         self._ref = ctypes.byref(self.layout)
+
+    def _plane(self, offset: int, dim: int) -> torch.Tensor:
+        flat = self.pool.view(self.pool.shape[0], -1)
+        start = self.layout.entry_offset + offset
+        return flat[:, start:start + self.kv_heads * self.page_size * dim].view(-1, self.kv_heads, self.page_size, dim)
+
+    def keys(self) -> torch.Tensor:
+        """This entry's key rows as a view ``[pages + 1][kv_heads][page_size][head_dim]``."""
+        return self._plane(0, self.head_dim)
+
+    def values(self) -> torch.Tensor:
+        """Its value rows ``[pages + 1][kv_heads][page_size][v_dim]`` (the key rows with one plane)."""
+        return self._plane(self.layout.v_offset, self.v_dim)
 
 
 def embed(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
@@ -145,8 +175,9 @@ def rope_kv_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions: t
     partial sums; they are folded here (with the bias) and ``qkv`` itself is not read."""
     _dev(qkv, table, positions, token_slot, q_out, kv.pool)
     n = q_out.shape[0]
-    if qkv.dtype != torch.float32 or qkv.shape[1] != (heads + 2 * kv.kv_heads) * kv.head_dim:
-        raise ValueError("rope_kv_write reads float32 [n][(heads + 2 kv_heads) * head_dim]")
+    width = (heads + kv.kv_heads) * kv.head_dim + (kv.kv_heads * kv.v_dim if kv.planes == 2 else 0)
+    if qkv.dtype != torch.float32 or qkv.shape[1] != width:
+        raise ValueError("rope_kv_write reads float32 [n][(heads + kv_heads) * head_dim + kv_heads * v_dim]")
     if q_out.dtype != kv.pool.dtype:
         raise TypeError("queries and the cache have one dtype")
     if pending is not None:
@@ -183,10 +214,22 @@ def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
     check(lib.cuda().axon_convert(_ptr(src), dtype_code(src), _ptr(dst), dtype_code(dst), src.numel(), _stream()))
 
 
-def argmax(logits: torch.Tensor, best: torch.Tensor) -> None:
-    _dev(logits, best)
-    rows, vocab = logits.shape
-    check(lib.cuda().axon_argmax(_ptr(logits), _ptr(best), rows, vocab, logits.stride(0), _stream()))
+def argmax(logits: torch.Tensor, best: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """best[r] = the id of the largest logit of row r, or of row ``rows[r]`` when given."""
+    _dev(logits, best, rows)
+    n, vocab = best.shape[0], logits.shape[1]
+    if rows is None:
+        check(lib.cuda().axon_argmax(_ptr(logits), _ptr(best), n, vocab, logits.stride(0), _stream()))
+    else:
+        check(lib.cuda().axon_argmax_rows(_ptr(logits), _ptr(rows), _ptr(best), n, vocab, logits.stride(0), _stream()))
+
+
+def gather_rows(src: torch.Tensor, rows: Optional[torch.Tensor], dst: torch.Tensor) -> None:
+    """dst[r] = src[rows[r]] (float32 rows; ``rows`` None copies them in order)."""
+    _dev(src, rows, dst)
+    if src.dtype != torch.float32 or dst.dtype != torch.float32 or dst.shape[1] != src.shape[1]:
+        raise ValueError("gather_rows copies float32 rows of one width")
+    check(lib.cuda().axon_gather_rows(_ptr(src), _ptr(rows), _ptr(dst), dst.shape[0], dst.shape[1], src.stride(0), _stream()))
 
 
 def repeat_penalty(logits: torch.Tensor, ids: torch.Tensor, penalty: torch.Tensor) -> None:
@@ -200,18 +243,19 @@ def topk_max() -> int:
     return lib.cuda().axon_topk_max()
 
 
-def topk(logits: torch.Tensor, ks: torch.Tensor, cand_logit: torch.Tensor, cand_id: torch.Tensor) -> None:
-    _dev(logits, ks, cand_logit, cand_id)
-    rows, vocab = logits.shape
-    check(lib.cuda().axon_topk(_ptr(logits), _ptr(ks), _ptr(cand_logit), _ptr(cand_id), rows, vocab,
+def topk(logits: torch.Tensor, ks: torch.Tensor, cand_logit: torch.Tensor, cand_id: torch.Tensor,
+         rows: Optional[torch.Tensor] = None) -> None:
+    _dev(logits, ks, cand_logit, cand_id, rows)
+    n, vocab = ks.shape[0], logits.shape[1]
+    check(lib.cuda().axon_topk(_ptr(logits), _ptr(rows), _ptr(ks), _ptr(cand_logit), _ptr(cand_id), n, vocab,
                                logits.stride(0), _stream()))
 
 
 def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
-                       picked: torch.Tensor) -> None:
-    _dev(logits, temperature, uniform, picked)
-    rows, vocab = logits.shape
+                       picked: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    _dev(logits, temperature, uniform, picked, rows)
+    n, vocab = picked.shape[0], logits.shape[1]
     if uniform.dtype != torch.float64 or temperature.dtype != torch.float32:
         raise TypeError("temperatures are float32, uniform numbers float64")
-    check(lib.cuda().axon_sample_temperature(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(picked), rows,
+    check(lib.cuda().axon_sample_temperature(_ptr(logits), _ptr(rows), _ptr(temperature), _ptr(uniform), _ptr(picked), n,
                                              vocab, logits.stride(0), _stream()))

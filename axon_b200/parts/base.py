@@ -13,6 +13,9 @@ Categories and what each must offer:
                ``compute(h, ctx, cache) -> tensor`` instead and inherit the add.
 ``ffn``        ``forward(h, x, ctx)``: as a mixer, without a cache.
 ``block``      ``forward(x, ctx, cache, write_cache)``: one layer on the residual stream.
+               ``cache`` is what the layer's cache-keeping parts own: the one view or slab
+               when one nested part answers ``cache_need``, a dict by part name (``"mixer"``,
+               dotted for deeper nesting) when several do, None when none does.
 ``embedding``  ``forward(tokens, x)``: token ids to float32 rows.
 ``head``       ``forward(h, logits)``: normed rows to float32 logits.
 

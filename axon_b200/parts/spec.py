@@ -90,12 +90,25 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class KvNeed:
-    """Keys and values in pages: ``kv_heads * head_dim`` elements of each per
-    token; ``window`` None keeps every position, else only the last ``window``."""
+    """Rows in pages, per token and kv head: a key row of ``head_dim`` elements and, with
+    ``planes`` 2, a value row of ``v_dim`` (None: as wide as the key).  ``planes`` 1 keeps one
+    row only (a latent that serves as key and value).  ``window`` None keeps every position,
+    else only the last ``window``."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
+    planes: int = 2
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.planes == 1 or not self.v_dim else self.v_dim
+
+    @property
+    def elements_per_token(self) -> int:
+        """Cache elements one position takes in one schedule entry."""
+        return self.kv_heads * (self.head_dim + (self.value_dim if self.planes == 2 else 0))
 
 
 @dataclass(frozen=True)

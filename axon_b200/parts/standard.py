@@ -147,10 +147,17 @@ class Attention(Mixer):
         self.position = build(spec.parts["position"]) if "position" in spec.parts else None
 
     def graph_key(self, ctx: StepContext):
+        """The split count of the decode-shape attention, which follows the longest context among
+        the segments short enough for that shape (every segment, in a step of single tokens)."""
         if self.rt.precise:
             return ()
         from ..kernels import fast
-        return (("key_splits", fast.decode_split_count(len(ctx.seg_slot), self.kv_heads, ctx.max_kv_len)),)
+        group = self.heads // self.kv_heads
+        fits = 16 // group if group <= 16 else 0
+        short = [kv for n, kv in zip(ctx.seg_q_len, ctx.seg_kv_len) if n <= fits]
+        if not short:
+            return ()
+        return (("key_splits", fast.decode_split_count(len(short), self.kv_heads, max(short))),)
 
     def forward(self, h, x, ctx: StepContext, cache: ops.KvView, write_cache: bool = True, defer: bool = False):
         rt, n = self.rt, ctx.n_tokens

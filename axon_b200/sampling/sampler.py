@@ -146,77 +146,92 @@ def pick_tokens(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
 
     Greedy rows take the device argmax (the last index among equal maxima).  Sampled
     rows get the penalty and the k best candidates on the device and the draw on the
-    host; the picked token is appended to the row's history.
+    host; the picked token is appended to the row's history.  Rows of one kind are read
+    where they lie (the kernels take a row index); only rows that the penalty changes are
+    copied first, by a kernel of this library.  Everything the kernels need from the host
+    (row indices, k, penalties, penalised ids, temperatures, uniform numbers) goes to the
+    device in one copy.
     """
     n, vocab = logits.shape
     assert n == len(rows)
+    if not logits.is_contiguous():
+        raise ValueError("pick_tokens takes contiguous logits")
     dev = logits.device
     out: List[Optional[int]] = [None] * n
     greedy = [i for i, r in enumerate(rows) if r.greedy]
     plain = [i for i, r in enumerate(rows) if not r.greedy and r.plain_temperature()]
     cand = [i for i, r in enumerate(rows) if not r.greedy and not r.plain_temperature()]
     kmax = ops.topk_max()
+    host = lib.host()
 
+    id_lists = []
+    for i in cand:
+        c = rows[i].cfg
+        id_lists.append(host.penalty_ids(rows[i].history, c.repeat_last_n)
+                        if (c.repeat_penalty != 1.0 and c.repeat_last_n > 0) else [])
+    width = max((len(x) for x in id_lists), default=0)
+    ks = [rows[i].cfg.top_k for i in cand]
+    on_device = [j for j, k in enumerate(ks) if 0 < k <= kmax]
+    ng, npl, nc = len(greedy), len(plain), len(cand)
+    # layout of the one upload, in 32-bit words: row indices of the three kinds | k | penalty
+    # (float bits) | penalised ids | temperatures (float bits) | pad to 8 bytes | uniforms (double)
+    o_k = ng + npl + nc
+    o_pen, o_ids = o_k + nc, o_k + 2 * nc
+    o_temp = o_ids + nc * width
+    o_uni = (o_temp + npl + 1) // 2 * 2
+    flat = np.full(o_uni + 2 * npl, -1, dtype=np.int32)
+    flat[:o_k] = greedy + plain + cand
+    keep = set(on_device)
+    flat[o_k:o_pen] = [ks[j] if j in keep else 0 for j in range(nc)]
+    flat[o_pen:o_ids] = np.asarray([rows[i].cfg.repeat_penalty for i in cand], dtype=np.float32).view(np.int32)
+    for j, ids in enumerate(id_lists):
+        flat[o_ids + j * width: o_ids + j * width + len(ids)] = ids
+    flat[o_temp:o_temp + npl] = np.asarray([rows[i].cfg.temp for i in plain], dtype=np.float32).view(np.int32)
+    flat[o_uni:] = np.asarray([rows[i].host.uniform() for i in plain], dtype=np.float64).view(np.int32)
+    up = torch.from_numpy(flat).to(dev)
+    whole = lambda idx: None if len(idx) == n else idx       # every row, in order: no index needed
+
+    picks = torch.empty(ng + npl, dtype=torch.int32, device=dev)
     if greedy:
-        sub = logits if len(greedy) == n else logits[torch.tensor(greedy, device=dev)].contiguous()
-        best = torch.empty(len(greedy), dtype=torch.int32, device=dev)
-        ops.argmax(sub, best)
-        for i, t in zip(greedy, best.tolist()):
-            out[i] = int(t)
+        ops.argmax(logits, picks[:ng], rows=whole(up[:ng]))
     if plain:
-        sub = logits if len(plain) == n else logits[torch.tensor(plain, device=dev)].contiguous()
-        # temperatures and uniforms in one host-to-device copy (each small copy costs a synchronisation)
-        both = torch.tensor([[rows[i].cfg.temp for i in plain], [rows[i].host.uniform() for i in plain]],
-                            dtype=torch.float64, device=dev)
-        temps, us = both[0].float(), both[1].contiguous()
-        picked = torch.empty(len(plain), dtype=torch.int32, device=dev)
-        ops.sample_temperature(sub, temps, us, picked)
-        for i, t in zip(plain, picked.tolist()):
-            out[i] = int(t)
+        ops.sample_temperature(logits, up[o_temp:o_temp + npl].view(torch.float32), up[o_uni:].view(torch.float64),
+                               picks[ng:], rows=whole(up[ng:ng + npl]))
+    both = None
+    sub = None
     if cand:
-        # a copy: the penalty writes into it
-        sub = logits.clone() if len(cand) == n else logits[torch.tensor(cand, device=dev)].contiguous()
-        host = lib.host()
-        id_lists = []
-        for i in cand:
-            c = rows[i].cfg
-            ids = host.penalty_ids(rows[i].history, c.repeat_last_n) if (c.repeat_penalty != 1.0 and c.repeat_last_n > 0) else []
-            id_lists.append(ids)
-        width = max((len(x) for x in id_lists), default=0)
-        ks = [rows[i].cfg.top_k for i in cand]
-        on_device = [j for j, k in enumerate(ks) if 0 < k <= kmax]
-        # the rows' k, penalty (float bits) and penalised ids in one host-to-device copy
-        # (each small copy costs a synchronisation)
-        nc = len(cand)
-        flat = np.full(nc * (2 + width), -1, dtype=np.int32)
-        keep = set(on_device)
-        flat[:nc] = [ks[j] if j in keep else 0 for j in range(nc)]
-        flat[nc:2 * nc] = np.asarray([rows[i].cfg.repeat_penalty for i in cand], dtype=np.float32).view(np.int32)
-        for j, ids in enumerate(id_lists):
-            flat[2 * nc + j * width: 2 * nc + j * width + len(ids)] = ids
-        flat_dev = torch.from_numpy(flat).to(dev)
+        if width or len(on_device) < nc:
+            # a copy: the penalty writes into it (and rows sorted on the host are read from it)
+            sub = torch.empty((nc, vocab), dtype=torch.float32, device=dev)
+            ops.gather_rows(logits, whole(up[ng + npl:o_k]), sub)
         if width:
-            ops.repeat_penalty(sub, flat_dev[2 * nc:].view(nc, width), flat_dev[nc:2 * nc].view(torch.float32))
+            ops.repeat_penalty(sub, up[o_ids:o_temp].view(nc, width), up[o_pen:o_ids].view(torch.float32))
         if on_device:
-            kt = flat_dev[:nc]
-            both = torch.empty((2, len(cand), kmax), dtype=torch.int32, device=dev)   # logits and ids: one copy back
-            cl, ci = both[0].view(torch.float32), both[1]
-            ops.topk(sub, kt, cl, ci)
-            both_h = both.cpu().numpy()
-            cl_h, ci_h = both_h[0].view(np.float32), both_h[1]
-            for j in on_device:
-                k = min(ks[j], vocab)
-                out[cand[j]] = int(rows[cand[j]].host.pick(cl_h[j, :k], ci_h[j, :k]))
-        for j, k in enumerate(ks):
-            if 0 < k <= kmax:
-                continue
-            # top-k off or above what the device selects: the whole row, sorted on the host
-            # (the reference's slower path, src/sample.rs:16-20)
-            row = sub[j].cpu().numpy()
-            order = _sorted_candidates(row)
-            if k > 0:
-                order = order[:k]
-            out[cand[j]] = int(rows[cand[j]].host.pick(row[order], order.astype(np.int32)))
+            both = torch.empty((2, nc, kmax), dtype=torch.int32, device=dev)   # logits and ids: one copy back
+            if sub is not None:
+                ops.topk(sub, up[o_k:o_pen], both[0].view(torch.float32), both[1])
+            else:
+                ops.topk(logits, up[o_k:o_pen], both[0].view(torch.float32), both[1], rows=whole(up[ng + npl:o_k]))
+    if greedy or plain:
+        got = picks.tolist()
+        for i, t in zip(greedy + plain, got):
+            out[i] = int(t)
+    if both is not None:
+        both_h = both.cpu().numpy()
+        cl_h, ci_h = both_h[0].view(np.float32), both_h[1]
+        for j in on_device:
+            k = min(ks[j], vocab)
+            out[cand[j]] = int(rows[cand[j]].host.pick(cl_h[j, :k], ci_h[j, :k]))
+    for j, k in enumerate(ks):
+        if 0 < k <= kmax:
+            continue
+        # top-k off or above what the device selects: the whole row, sorted on the host
+        # (the reference's slower path, src/sample.rs:16-20)
+        row = sub[j].cpu().numpy()
+        order = _sorted_candidates(row)
+        if k > 0:
+            order = order[:k]
+        out[cand[j]] = int(rows[cand[j]].host.pick(row[order], order.astype(np.int32)))
     for i, r in enumerate(rows):
         r.history.append(out[i])
     return [int(t) for t in out]

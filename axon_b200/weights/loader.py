@@ -86,29 +86,43 @@ def _device_dtype(stored: torch.dtype, kind: str, model_dtype: torch.dtype) -> t
     return torch.bfloat16
 
 
+def check_checkpoint(ckpt: Checkpoint, spec: ModelSpec, where: str) -> Dict[str, TensorDecl]:
+    """Compare a checkpoint's tensors (names, shapes, dtypes; no data is read) with what the
+    model needs; raises one :class:`WeightsError` that lists every fault, else returns the
+    model's tensors by checkpoint name."""
+    want = expected_tensors(spec)
+    have = ckpt.infos
+    ignored = lambda n: any(n.endswith(s) for s in spec.ignored_suffixes)
+    missing = sorted(n for n in want if n not in have)
+    unexpected = sorted(n for n in have if n not in want and not ignored(n))
+    shapes = [(n, have[n].shape, want[n].shape) for n in sorted(want)
+              if n in have and tuple(have[n].shape) != tuple(want[n].shape)]
+    dtypes = [(n, have[n].dtype) for n in sorted(want)
+              if n in have and have[n].dtype not in ("BF16", "F16", "F32")]
+    if missing or unexpected or shapes or dtypes:
+        raise WeightsError(where, missing, unexpected, shapes, dtypes)
+    return want
+
+
 def load_weights(folder: str, spec: ModelSpec, dtype: torch.dtype,
                  device: Union[str, torch.device]) -> Dict[str, torch.Tensor]:
-    """Read the model's tensors from ``folder`` onto ``device``."""
-    want = expected_tensors(spec)
+    """Read the model's tensors from ``folder`` onto ``device``.  A tensor goes from the
+    mapped file to the device in one copy (no staging copy on the host), and is converted
+    there, so the host never holds more than the mapping."""
+    ckpt = Checkpoint(folder)
     try:
-        ckpt = Checkpoint(folder)
-    except SafetensorsError:
-        raise
-    try:
-        have = ckpt.infos
-        ignored = lambda n: any(n.endswith(s) for s in spec.ignored_suffixes)
-        missing = sorted(n for n in want if n not in have)
-        unexpected = sorted(n for n in have if n not in want and not ignored(n))
-        shapes = [(n, have[n].shape, want[n].shape) for n in sorted(want)
-                  if n in have and tuple(have[n].shape) != tuple(want[n].shape)]
-        dtypes = [(n, have[n].dtype) for n in sorted(want)
-                  if n in have and have[n].dtype not in ("BF16", "F16", "F32")]
-        if missing or unexpected or shapes or dtypes:
-            raise WeightsError(folder, missing, unexpected, shapes, dtypes)
+        want = check_checkpoint(ckpt, spec, folder)
         out: Dict[str, torch.Tensor] = {}
         for name, decl in want.items():
-            t = ckpt.tensor(name)
-            out[name] = t.to(device=device, dtype=_device_dtype(t.dtype, decl.kind, dtype)).contiguous()
+            t = ckpt.tensor(name, copy=False)
+            want_dt = _device_dtype(t.dtype, decl.kind, dtype)
+            d = t.to(device=device)
+            if d.data_ptr() == t.data_ptr():
+                d = t.clone()                   # the same memory (a host "device"): the mapping will be closed
+            out[name] = d.to(want_dt).contiguous()
+            del t, d
+        if torch.device(device).type == "cuda":
+            torch.cuda.synchronize(device)      # the copies read the mapping: done before it is closed
         return out
     finally:
         ckpt.close()

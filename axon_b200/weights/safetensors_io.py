@@ -119,19 +119,28 @@ class SafetensorsFile:
             self._map = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
         return self._map
 
-    def tensor(self, name: str) -> torch.Tensor:
-        """A copy of the tensor's data on the host, in its stored dtype."""
+    def tensor(self, name: str, copy: bool = True) -> torch.Tensor:
+        """The tensor on the host, in its stored dtype.  With ``copy`` false it is a read-only
+        view of the mapped file (no bytes are copied; it must not be written to and is valid
+        until ``close``): what a loader wants that only copies the tensor on to a device."""
         info = self.infos[name]
         dtype, _ = _DTYPES[info.dtype]
         if info.end == info.begin:
             return torch.empty(info.shape, dtype=dtype)
         m = self._mapped()
-        raw = bytes(m[self.data_offset + info.begin: self.data_offset + info.end])
-        return torch.frombuffer(bytearray(raw), dtype=dtype).reshape(info.shape)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # torch warns that the buffer is read-only
+            t = torch.frombuffer(m, dtype=dtype, count=(info.end - info.begin) // _DTYPES[info.dtype][1],
+                                 offset=self.data_offset + info.begin).reshape(info.shape)
+        return t.clone() if copy else t
 
     def close(self) -> None:
         if self._map is not None:
-            self._map.close()
+            try:
+                self._map.close()
+            except BufferError:
+                pass          # a view handed out by tensor(copy=False) still lives: freed with it
             self._map = None
         self._f.close()
 
@@ -181,8 +190,8 @@ class Checkpoint:
     def names(self) -> Iterable[str]:
         return self.infos.keys()
 
-    def tensor(self, name: str) -> torch.Tensor:
-        return self._by_path[self.infos[name].file].tensor(name)
+    def tensor(self, name: str, copy: bool = True) -> torch.Tensor:
+        return self._by_path[self.infos[name].file].tensor(name, copy)
 
     def close(self) -> None:
         for f in self.files.values():

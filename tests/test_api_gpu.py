@@ -119,6 +119,45 @@ def test_continuous_batching_with_too_few_pages(model_folders):
     assert net.engine.cache.manager.n_open == 0
 
 
+def test_sampled_requests_survive_preemption(model_folders):
+    """Greedy and sampled requests (different seeds, k, penalties; one drawing on the device, one
+    sorted on the host) share four slots and a pool too small for them: some are preempted and
+    fed again with their sampler state kept, and every request's tokens equal those of the
+    same request run alone (the reference's test: src/cuda/qwen2/slots.rs:1622-1796)."""
+    import axon_b200 as axon
+    from axon_b200.engine.serve import BatchRunner
+    folder = model_folders["B"]
+    prompts = [prompt_for("B", 40 + i, n) for i, n in enumerate([30, 5, 44, 17, 9, 25, 3, 38])]
+    n_gen = [30, 40, 20, 35, 12, 28, 45, 16]
+    cfgs = [None,
+            axon.SampleCfg(temp=0.8, seed=21),
+            axon.SampleCfg(temp=1.0, top_k=5, top_p=1.0, repeat_penalty=1.0, seed=22),
+            None,
+            axon.SampleCfg(temp=1.3, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0, seed=23),      # device draw
+            axon.SampleCfg(temp=0.7, top_k=300, top_p=0.95, min_p=0.01, repeat_penalty=1.3, seed=24),  # host-sorted
+            axon.SampleCfg(temp=0.9, top_k=40, top_p=0.9, repeat_penalty=1.2, repeat_last_n=8, seed=25),
+            None]
+    roomy = axon.Backend(axon.load(folder), axon.BackendOptions().max_ctx(128).dtype("float32").parallel(2))
+    alone = []
+    for p, n, c in zip(prompts, n_gen, cfgs):
+        with roomy.new_cache() as cache:
+            logits = roomy.prefill_logits(p, 0, cache)
+            opts = axon.GenOpts.greedy(n, []) if c is None else axon.GenOpts.sampled(n, [], c)
+            alone.append(axon.generate(roomy, cache, p, logits, opts).ids)
+    opts = axon.BackendOptions().max_ctx(96).dtype("float32").parallel(4).kv_tokens(160).step_tokens(24)
+    net = axon.Backend(axon.load(folder), opts)
+    runner = BatchRunner(net.engine, max_batch_tokens=24, max_running=4, prefill_chunk=16)
+    for i, (p, n, c) in enumerate(zip(prompts, n_gen, cfgs)):
+        runner.add(i, p, n, (), c)
+    outs = runner.run()
+    assert runner.preemptions > 0, "the pool was meant to be too small"
+    for i in range(len(prompts)):
+        assert outs[i] == alone[i], f"request {i} ({'greedy' if cfgs[i] is None else 'sampled'})"
+    net.engine.cache.manager.check()
+    net.engine.cache.flush()
+    assert net.engine.cache.manager.free_pages(0) == net.engine.cache.n_pages
+
+
 def test_command_line(model_folders):
     cfg, w = plain.read_model(model_folders["B"])
     ids = prompt_for("B", 3, 12)
@@ -140,4 +179,5 @@ def test_command_line(model_folders):
     p = subprocess.run([axon, "gen", model_folders["B"], "1 2", "--temp", "7000"], capture_output=True, text=True, timeout=600)
     assert p.returncode == 2 and "--temp needs a number from 0 to 100" in p.stderr
     p = subprocess.run([axon, "info", model_folders["B"]], capture_output=True, text=True, timeout=600)
-    assert p.returncode == 0 and "layers 3 / dim 96 / heads 3 (kv 1)" in p.stdout
+    assert p.returncode == 0 and "layers 3 (schedule of 3 runs) / dim 96 / vocab 384 / ctx 256" in p.stdout
+    assert "num_key_value_heads 1" in p.stdout and "3 x prenorm(" in p.stdout

@@ -188,3 +188,42 @@ def test_staged_decode_step_matches_the_calls_it_replaces(host):
     m3.commit(a, 4); m3.commit(b, 8)
     rc, bad = m3.stage_decode([a, b], [1, 1], [1, 1], 100, out)
     assert (rc, bad) == (2, 0)
+
+
+def test_pool_sized_from_free_memory():
+    """The arithmetic of the automatic pool size (the reference's rule, src/serve.rs:2411-2449):
+    free memory less workspace and reserve, in whole pages, one page kept for the sink, and never
+    more than every slot at full context needs."""
+    from axon_b200.cache.manager import POOL_RESERVE_BYTES, plan_pool_tokens
+    per_token, page = 57344, 16              # the 7B shape in bfloat16
+    # plenty of memory: capped by slots x context (rounded up to pages)
+    assert plan_pool_tokens(160 << 30, per_token, page, 64, 4096) == 64 * 4096
+    assert plan_pool_tokens(160 << 30, per_token, page, 3, 100) == 3 * 112
+    # little memory: what fits, less the sink page
+    free = POOL_RESERVE_BYTES + 10 * page * per_token + 5
+    assert plan_pool_tokens(free, per_token, page, 64, 4096) == 9 * page
+    assert plan_pool_tokens(free, per_token, page, 64, 4096, workspace_bytes=4 * page * per_token) == 5 * page
+    # nothing fits: zero, which the builder turns into an error
+    assert plan_pool_tokens(POOL_RESERVE_BYTES, per_token, page, 64, 4096) == 0
+    assert plan_pool_tokens(0, per_token, page, 64, 4096) == 0
+    # a model that keeps no keys and values needs no memory per position
+    assert plan_pool_tokens(0, 0, page, 4, 64) == 4 * 64
+
+
+def test_needs_by_part_name_make_groups_and_views():
+    """A schedule entry may hold several cache-keeping parts (by name), parts of equal geometry
+    share a group, and a part with one plane or another value width gets a group of its own."""
+    import torch
+    from axon_b200.cache.manager import PagedCache, bytes_per_token
+    from axon_b200.parts.spec import KvNeed, StateNeed
+    a, b = KvNeed(2, 16), KvNeed(2, 16, window=8)
+    latent = KvNeed(1, 24, planes=1)
+    wide_v = KvNeed(2, 16, v_dim=40)
+    needs = [{"mixer": a}, {"attn": a, "memory": StateNeed((4,), "float32")}, {}, None, {"mixer": b},
+             {"mixer": latent}, wide_v, {"x": wide_v, "y": a}]
+    c = PagedCache(needs, torch.bfloat16, "cpu", page_size=16, max_tokens=64, max_slots=2, allocate=False)
+    assert [len(g.members) for g in c.groups] == [3, 1, 1, 2]
+    assert c.groups[0].members == [(0, "mixer"), (1, "attn"), (7, "y")]
+    assert c.parts(1) == ["attn", "memory"] and c.parts(2) == [] and c.parts(6) == ["mixer"]
+    assert latent.elements_per_token == 24 and wide_v.elements_per_token == 2 * (16 + 40)
+    assert bytes_per_token(needs, torch.bfloat16) == 2 * (4 * 64 + 24 + 2 * 112)

@@ -407,3 +407,215 @@ def test_trace_run_program(model_folders, plain_models, tmp_path, dtype):
     check_rows(got2, [want[75], want[4]], TOL[dtype], "trace_run step 2")
     got3 = torch.from_numpy(np.fromfile(out / "3.f32", dtype="<f4").reshape(-1, V)).double()
     check_rows(got3, [want[76]], TOL[dtype], "trace_run step 3")
+
+
+# ---------------------------------------------------------------------------
+# The schedule that serving and the bench run: many live requests decoding one token a
+# step through replayed CUDA graphs, key splits that change as contexts grow and as
+# requests leave and join, shuffled pages that are used again.
+
+LONG = {
+    # head size 128 (the tcgen05 prompt kernel, the fused decode kernel), 2 kv heads
+    "C": dict(TINY["C"], max_position_embeddings=1536),
+    # head size 32, one kv head
+    "B": dict(TINY["B"], max_position_embeddings=1536),
+}
+
+
+@pytest.fixture(scope="module")
+def long_folders(tmp_path_factory):
+    from conftest import make_model_folder
+    return {k: make_model_folder(str(tmp_path_factory.mktemp(f"long_{k}")), cfg, 4321 + i)
+            for i, (k, cfg) in enumerate(LONG.items())}
+
+
+def _long_tokens(name, i, n):
+    g = torch.Generator().manual_seed(50_000 + 1000 * (ord(name) - 64) + i)
+    return torch.randint(0, LONG[name]["vocab_size"], (n,), generator=g).tolist()
+
+
+def _many_requests_schedule(name, n_first=24, n_late=4, decode_steps=80):
+    """(requests, steps): request r = (tokens, prompt length, first decode step, last decode step).
+    The first 24 hold contexts spread over 300..1200 when decoding starts; four of them (the
+    longest among them) end early and four others join on the pages that came free."""
+    reqs = {}
+    for r in range(n_first):
+        ctx = 300 + (r * 900) // (n_first - 1)
+        last = decode_steps - 1
+        if r in (n_first - 1, n_first - 2):       # the two longest leave at steps 25 and 40
+            last = 24 if r == n_first - 1 else 39
+        elif r in (3, 11):
+            last = 31
+        reqs[r] = (ctx, 0, last)
+    for j in range(n_late):
+        reqs[n_first + j] = (350 + 130 * j, 33 + 8 * j, decode_steps - 1)
+    toks = {r: _long_tokens(name, r, ctx + (last - first + 1)) for r, (ctx, first, last) in reqs.items()}
+    return reqs, toks
+
+
+def _run_many(engine, name, reqs, toks, decode_steps, greedy):
+    """Feed prompts (whole, no logits wanted), then one token per live request per step.
+    Returns {(request, position): row or pick} and the split counts the decode steps used."""
+    from axon_b200.engine.step import StepEntry
+    from axon_b200.kernels import fast
+    slots, out, splits_seen, replays = {}, {}, [], 0
+    kv_heads = LONG[name]["num_key_value_heads"]
+    for t in range(decode_steps):
+        for r, (ctx, first, last) in reqs.items():
+            if first == t:
+                slots[r] = engine.open_request()
+                engine.step([StepEntry(slots[r], toks[r][:ctx], [])])
+        live = [r for r, (ctx, first, last) in reqs.items() if first <= t <= last]
+        entries, where = [], []
+        for r in live:
+            ctx, first, _ = reqs[r]
+            pos = ctx + (t - first)
+            entries.append(StepEntry(slots[r], [toks[r][pos]], [0]))
+            where.append((r, pos))
+        if engine.rt.dtype == torch.bfloat16:
+            splits_seen.append(fast.decode_split_count(len(live), kv_heads, max(p for _, p in where) + 1))
+        before = len(engine._graphs)
+        res = engine.step(entries, greedy=greedy)
+        replays += len(engine._graphs) == before
+        res = res.cpu()
+        for k, key in enumerate(where):
+            out[key] = int(res[k]) if greedy else res[k].double()
+        for r in live:
+            if reqs[r][2] == t:
+                engine.close_request(slots.pop(r))
+    return out, splits_seen, replays
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "B"])
+def test_many_requests_decoding_through_replayed_graphs(long_folders, name, dtype):
+    """24 live requests at contexts of 300 to 1,200 decode 80 tokens, each step's logits against
+    the plain implementation; requests leave and others join on their (shuffled) pages; in
+    bfloat16 the steps are replayed CUDA graphs whose key-split count changes several times."""
+    steps = 80
+    reqs, toks = _many_requests_schedule(name)
+    cfg, w = plain.read_model(long_folders[name])
+    # the pool holds what is live at the worst moment, so the late requests reuse freed pages
+    worst = 0
+    for t in range(steps):
+        live = sum(-(-(ctx + (min(t, last) - first + 1)) // 16) * 16 for ctx, first, last in reqs.values() if first <= t <= last)
+        worst = max(worst, live)
+    total = sum(-(-len(v) // 16) * 16 for v in toks.values())
+    assert worst < total
+    logits = None
+    for greedy in (False, True):
+        engine = build(long_folders[name], dtype, max_tokens=worst, page_size=16, max_slots=32, max_positions=1536,
+                       shuffle_seed=5, max_step_tokens=2048)
+        got, splits_seen, replays = _run_many(engine, name, reqs, toks, steps, greedy)
+        if dtype == "bfloat16":
+            assert len(set(splits_seen)) >= 3 and max(splits_seen) > 1, f"split counts {sorted(set(splits_seen))}"
+            assert engine.cuda_graphs and replays >= steps // 2, f"{replays} of {steps} steps replayed a graph"
+        if not greedy:
+            logits = got
+            want = {r: plain.forward(cfg, w, toks[r]) for r in reqs}
+            worst_err = 0.0
+            for (r, pos), row in got.items():
+                ref = want[r][pos]
+                scale = float(want[r].abs().max())
+                err = float((row - ref).abs().max()) / scale
+                worst_err = max(worst_err, err)
+                assert err <= TOL[dtype], f"{name}/{dtype} request {r} position {pos}: {err:.2e} of the scale"
+            assert len(got) == sum(last - first + 1 for _, first, last in reqs.values())
+        else:
+            # the pick inside the graph is the argmax of the same step's logits
+            for key, pick in got.items():
+                row = logits[key]
+                assert pick == int((row == row.max()).nonzero().max()), f"{name}/{dtype} {key}"
+        engine.cache.manager.check()
+        engine.cache.flush()
+        assert engine.cache.manager.free_pages(0) == engine.cache.n_pages, "pages were lost"
+        del engine
+        torch.cuda.empty_cache()
+
+
+def test_more_decoding_requests_than_the_fused_attention_takes(tmp_path):
+    """60 requests over 8 kv heads are 480 (request, kv head) pairs: more CTAs than the decode
+    attention that rotates and writes by itself is used for, so the step takes the rotation
+    kernel and the attention kernel.  Every request's logits against the plain implementation,
+    through the captured graph."""
+    from conftest import make_model_folder
+    from axon_b200.engine.step import StepEntry
+    from axon_b200.kernels import fast
+    cfg = dict(TINY["A"], num_attention_heads=8, num_key_value_heads=8, head_dim=16, hidden_size=64,
+               max_position_embeddings=160, vocab_size=300, num_hidden_layers=2)
+    folder = make_model_folder(str(tmp_path / "wide_batch"), cfg, 31)
+    pcfg, w = plain.read_model(folder)
+    n_req, n_dec = 60, 6
+    assert n_req * 8 > 3 * fast.SM_COUNT
+    g = torch.Generator().manual_seed(9)
+    toks = [torch.randint(0, 300, (20 + (7 * r) % 90 + n_dec,), generator=g).tolist() for r in range(n_req)]
+    want = [plain.forward(pcfg, w, t) for t in toks]
+    for dtype in ("bfloat16", "float32"):
+        engine = build(folder, dtype, max_tokens=n_req * 128, page_size=16, max_slots=n_req, max_positions=160, shuffle_seed=3)
+        slots = [engine.open_request() for _ in range(n_req)]
+        for r in range(n_req):
+            engine.step([StepEntry(slots[r], toks[r][:-n_dec], [])])
+        for k in range(n_dec):
+            res = engine.step([StepEntry(slots[r], [toks[r][len(toks[r]) - n_dec + k]], [0]) for r in range(n_req)]).double().cpu()
+            for r in range(n_req):
+                pos = len(toks[r]) - n_dec + k
+                err = float((res[r] - want[r][pos]).abs().max()) / float(want[r].abs().max())
+                assert err <= TOL[dtype], f"{dtype} request {r} step {k}: {err:.2e}"
+        if dtype == "bfloat16":
+            assert engine.cuda_graphs and len(engine._graphs) >= 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_token_portions_at_short_and_long_contexts(long_folders, dtype):
+    """A portion of two tokens takes the decode-shape attention, whose key-split count follows the
+    context: the same portion size comes at a short context (captured as a graph from the
+    second time), then after a long stretch of prompt (another split count: another graph)."""
+    name = "C"
+    cfg, w = plain.read_model(long_folders[name])
+    n = 2 * 4 + 900 + 2 * 6
+    toks = _long_tokens(name, 77, n)
+    want = plain.forward(cfg, w, toks)
+    engine = build(long_folders[name], dtype, max_tokens=1024, page_size=16, max_slots=2, max_positions=1536)
+    tr, at = Trace(), 0
+    sizes = [2] * 4 + [900] + [2] * 6
+    for size in sizes:
+        tr.step([("r", ("x",), toks[at:at + size], [0, size - 1])], end=["r"] if at + size == n else [])
+        at += size
+    got = replay(engine, tr.steps)
+    at = 0
+    for k, size in enumerate(sizes):
+        check_rows(got[k], [want[at], want[at + size - 1]], TOL[dtype], f"{dtype} portion {k} of {size} at {at}")
+        at += size
+    if dtype == "bfloat16":
+        keys = [k for k in engine._graphs if k[0] == "portion" and k[1] == 2]
+        assert len({k[3] for k in keys}) >= 2, f"the split count belongs to a portion's graph key: {keys}"
+
+
+def test_steps_queued_without_waiting_keep_their_own_tables(model_folders):
+    """Steps are queued without the host ever waiting for one: a request ends, its slot is opened
+    again for another request and fed, while earlier steps' table copies may still be pending.
+    Every step must see the block table it was planned with: the results equal the same
+    steps run with a wait after each."""
+    from axon_b200.engine.step import StepEntry
+    name = "A"
+    outs = {}
+    for waited in (True, False):
+        engine = build(model_folders[name], "bfloat16", max_tokens=96, page_size=16, max_slots=2, shuffle_seed=2)
+        res = []
+        big = tokens_for(name, 90, 60)
+        for round_ in range(12):
+            a = engine.open_request()
+            # a long portion first, so that the device is behind the host
+            res.append(engine.step([StepEntry(a, big, [59])]).clone())
+            for k in range(3):
+                res.append(engine.step([StepEntry(a, [(7 * round_ + k) % 256], [0])]).clone())
+            engine.close_request(a)
+            b = engine.open_request()             # the same slot, pages handed out anew
+            res.append(engine.step([StepEntry(b, tokens_for(name, 91 + round_, 17), [16])]).clone())
+            res.append(engine.step([StepEntry(b, [round_], [0])]).clone())
+            engine.close_request(b)
+            if waited:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        outs[waited] = torch.cat(res)
+    assert torch.equal(outs[True], outs[False])

@@ -353,20 +353,10 @@ def test_residual_add_and_convert(ops, dtype):
 # ---------------------------------------------------------------------------
 # the tuned bfloat16 kernels, each against float64
 
-@pytest.fixture(params=["tcgen05_swapped", "mma_sync"])
-def small_m_kernel(request):
-    """Both kernels for at most 64 rows, one at a time."""
-    from axon_b200.kernels import fast
-    old = fast.ENABLED["gemm_tc_small"]
-    fast.ENABLED["gemm_tc_small"] = request.param == "tcgen05_swapped"
-    yield request.param
-    fast.ENABLED["gemm_tc_small"] = old
-
-
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 23, 32, 33, 64])
 @pytest.mark.parametrize("N,K", [(16, 64), (2, 8), (33, 24), (1000, 160), (344, 344), (130, 1096), (4608, 3584),
                                  (3584, 18944), (76032 + 6, 72)])
-def test_gemm_small_m(ops, small_m_kernel, M, N, K):
+def test_gemm_small_m(ops, M, N, K):
     from axon_b200.kernels import fast
     a = rand(M, K, dtype=torch.bfloat16, seed=70)
     w = rand(N, K, dtype=torch.bfloat16, seed=71, std=0.1)
@@ -627,15 +617,14 @@ def _ctx_for(segs):
 @pytest.mark.parametrize("heads,kv_heads,hd,ps,window", [
     (4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (6, 2, 64, 8, 0), (28, 4, 128, 16, 0), (8, 8, 128, 16, 0),
     (40, 2, 64, 16, 0), (7, 1, 128, 1, 0), (6, 2, 64, 16, 70), (4, 2, 128, 16, 9)])
-@pytest.mark.parametrize("fold,tcgen05", [("cluster", True), ("second_kernel", True), ("last_cta", True), ("cluster", False)])
+@pytest.mark.parametrize("fold,tcgen05", [("second_kernel", True), ("last_cta", True), ("second_kernel", False)])
 def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold, tcgen05, monkeypatch):
     """The tensor-core kernel on a mixed batch: decoded tokens at short and long contexts
     (one key; several splits), two-token portions, a whole prompt, a portion in the middle
     of a long request.  One key far back gets a large score so that a wrong page or a
     dropped tile shows."""
     from axon_b200.kernels import fast
-    # the three ways of folding the key splits of a decoded token
-    monkeypatch.setattr(fast, "FA_CLUSTER", fold == "cluster")
+    # the two ways of folding the key splits of a decoded token
     monkeypatch.setattr(fast, "FA_FOLD_IN_KERNEL", fold == "last_cta")
     # prompt portions at head size 128: the tcgen05 kernel, or the mma.sync one as for other head sizes
     monkeypatch.setitem(fast.ENABLED, "attention_tc", tcgen05)
@@ -795,3 +784,147 @@ def test_attention_tensor_core_refusals(ops):
     ctx = _ctx_for([(0, 1, 5)])
     q = rand(1, 2 * 48, dtype=torch.bfloat16)
     assert not fast.attention(q, view, ctx, torch.empty_like(q), 2, 0.1)       # head size 48: the plain kernel runs
+
+
+# ---------------------------------------------------------------------------
+# Caches whose key and value rows differ in width, and caches with one plane.
+
+def _odd_cache(ops, dtype, kv_heads, hd, v_dim, planes, ps, n_pages, slots, max_pos, entries=2, entry=1, seed=0):
+    from axon_b200.parts.spec import KvNeed
+    need = KvNeed(kv_heads, hd, None, v_dim if planes == 2 else None, planes)
+    stride = -(-max_pos // ps)
+    pool = torch.zeros(n_pages + 1, entries, ps * need.elements_per_token, dtype=dtype, device=DEV)
+    g = torch.Generator().manual_seed(seed)
+    table = torch.randperm(n_pages, generator=g)[: slots * stride].to(torch.int32).view(slots, stride).to(DEV)
+    return ops.KvView(pool, table, entry, ps, kv_heads, hd, 0, v_dim=need.value_dim, planes=planes), table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,v_dim,planes", [(4, 2, 16, 40, 2), (3, 1, 24, 8, 2), (4, 1, 32, 32, 1)])
+def test_plain_kernels_with_other_planes(ops, dtype, heads, kv_heads, hd, v_dim, planes):
+    """The rotate-and-write kernel and the plain attention on a cache whose value rows are wider or
+    narrower than its key rows, and on a cache with one plane (values read from the key rows)."""
+    n, ps = 9, 4
+    view, table = _odd_cache(ops, dtype, kv_heads, hd, v_dim, planes, ps, 6, 1, 12, seed=3)
+    vd = view.v_dim
+    width = (heads + kv_heads) * hd + (kv_heads * vd if planes == 2 else 0)
+    qkv = rand(n, width, seed=21)
+    positions = torch.arange(n, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(n, dtype=torch.int32, device=DEV)
+    q_out = torch.empty(n, heads * hd, dtype=dtype, device=DEV)
+    ops.rope_kv_write(qkv, None, positions, slots, q_out, view, heads, 0, False)
+    q = qkv[:, :heads * hd].view(n, heads, hd)
+    k = qkv[:, heads * hd:(heads + kv_heads) * hd].view(n, kv_heads, hd)
+    v = qkv[:, (heads + kv_heads) * hd:].view(n, kv_heads, vd) if planes == 2 else k
+    keys, values = view.keys(), view.values()
+    for t in range(n):
+        page = int(table[0, t // ps])
+        close(keys[page, :, t % ps], k[t], OUT_TOL[dtype], "key rows")
+        close(values[page, :, t % ps], v[t], OUT_TOL[dtype], "value rows")
+    assert float(view.pool[:, 0].abs().max()) == 0.0, "the other entry's planes were touched"
+    out = torch.empty(n, heads * vd, dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention_plain(q_out, view, positions, slots, out, heads, scale)
+    group = heads // kv_heads
+    kd, vdd = k.to(dtype).double(), v.to(dtype).double()
+    for t in range(n):
+        for h in range(heads):
+            w = torch.softmax((kd[: t + 1, h // group] @ q_out[t].view(heads, hd)[h].double()) * scale, 0)
+            close(out[t].view(heads, vd)[h], w @ vdd[: t + 1, h // group], OUT_TOL[dtype], f"token {t} head {h}")
+    # the tuned kernels refuse such a cache instead of misreading it
+    from axon_b200.kernels import fast
+    if dtype == torch.bfloat16:
+        assert not fast.attention(q_out, view, _ctx_for([(0, n, n)]), torch.empty_like(q_out), heads, scale)
+
+
+def test_checked_tables_catch_an_entry_outside_the_pool(ops):
+    """With checked tables a block-table entry beyond the pool is not followed: the kernel uses the
+    sink page and records the entry.  The "bad" entry here still lies inside the tensor (the
+    view is told that the pool is smaller than it is), so nothing could go astray either way."""
+    heads, kv_heads, hd, ps = 4, 2, 64, 16
+    real_pages, said_pages = 12, 6
+    pool = (torch.randn(real_pages + 1, 1, 2, kv_heads, ps, hd) * 0.5).to(torch.bfloat16).to(DEV)
+    table = torch.tensor([[0, 1, 2, 3], [4, 9, 5, said_pages]], dtype=torch.int32, device=DEV)    # 9 > 6: outside
+    fault = torch.zeros(2, dtype=torch.int32, device=DEV)
+    view = ops.KvView(pool[: said_pages + 1], table, 0, ps, kv_heads, hd, 0, fault=fault)
+    assert view.n_pages == said_pages
+    from axon_b200.kernels import fast
+    ctx = _ctx_for([(0, 1, 60), (1, 1, 40)])
+    q = rand(2, heads * hd, dtype=torch.bfloat16, seed=5)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    # the request whose table is fine: nothing recorded
+    ok = ops.KvView(pool[: said_pages + 1], table[:1].contiguous(), 0, ps, kv_heads, hd, 0, fault=fault)
+    assert fast.attention(q[:1].contiguous(), ok, _ctx_for([(0, 1, 60)]), out[:1], heads, scale)
+    assert fault.tolist() == [0, 0]
+    for run in ("tuned", "plain", "write"):
+        fault.zero_()
+        if run == "tuned":
+            assert fast.attention(q, view, ctx, out, heads, scale)
+        elif run == "plain":
+            ops.attention_plain(q, view, ctx.positions, ctx.token_slot, out, heads, scale)
+        else:
+            qkv = rand(1, (heads + 2 * kv_heads) * hd, seed=6)
+            ops.rope_kv_write(qkv, None, torch.tensor([20], dtype=torch.int32, device=DEV),
+                              torch.tensor([1], dtype=torch.int32, device=DEV), torch.empty_like(q[:1]), view, heads, 0)
+        assert fault.tolist() == [1, 9], f"{run}: the entry outside the pool was not recorded"
+    assert float(pool[9].float().abs().sum()) > 0 and torch.isfinite(out.float()).all()
+
+
+def test_a_wait_that_gives_up_sets_the_status_and_the_next_launch_works(ops):
+    """The failure path of the tensor-core product: its epilogue's wait for the accumulator is
+    never answered (a test mode of the launcher) and gives up after a few thousand polls.  The
+    kernel still ends in order, the status word says which role gave up, and once the word is
+    cleared the next launch gives the right product."""
+    from axon_b200.kernels import fast, lib
+    cu = lib.cuda()
+    M, N, K = 300, 512, 256
+    a = rand(M, K, dtype=torch.bfloat16, seed=80)
+    w = rand(N, K, dtype=torch.bfloat16, seed=81, std=0.1)
+    out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    old = fast.ENABLED["gemm_tc_small"]
+    fast.ENABLED["gemm_tc_small"] = False                 # the tiled kernel, whatever the row count
+    try:
+        assert fast.gemm_tc_status() == 0
+        cu.axon_gemm_tc_test_stuck_wait(4096)
+        try:
+            assert fast.gemm(a, w, out, None, False)
+            torch.cuda.synchronize()                      # the kernel returned by itself
+        finally:
+            cu.axon_gemm_tc_test_stuck_wait(0)
+        assert fast.gemm_tc_status() == 3, "1 + role 2: the epilogue's wait gave up"
+        assert cu.axon_gemm_tc_clear_status() == 0 and fast.gemm_tc_status() == 0
+        assert fast.gemm(a, w, out, None, False)
+        close(out, a.double() @ w.double().T, 2e-5, "the launch after the failure")
+        assert fast.gemm_tc_status() == 0
+    finally:
+        fast.ENABLED["gemm_tc_small"] = old
+
+
+def test_pickers_read_rows_by_index(ops):
+    """argmax, top-k and the temperature draw on some rows of a batch, named by an index, give what
+    they give on a copy of those rows."""
+    vocab = 1000
+    logits = rand(7, vocab, seed=3)
+    idx = torch.tensor([5, 0, 6], dtype=torch.int32, device=DEV)
+    sub = logits[idx.long()].contiguous()
+    a, b = torch.empty(3, dtype=torch.int32, device=DEV), torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, a, rows=idx)
+    ops.argmax(sub, b)
+    assert torch.equal(a, b) and a.tolist() == sub.argmax(1).tolist()
+    ks = torch.tensor([5, 40, 1], dtype=torch.int32, device=DEV)
+    kmax = ops.topk_max()
+    c1, i1 = torch.zeros(3, kmax, device=DEV), torch.zeros(3, kmax, dtype=torch.int32, device=DEV)
+    c2, i2 = torch.zeros(3, kmax, device=DEV), torch.zeros(3, kmax, dtype=torch.int32, device=DEV)
+    ops.topk(logits, ks, c1, i1, rows=idx)
+    ops.topk(sub, ks, c2, i2)
+    for r, k in enumerate(ks.tolist()):
+        assert torch.equal(c1[r, :k], c2[r, :k]) and torch.equal(i1[r, :k], i2[r, :k])
+    temps = torch.tensor([0.7, 1.0, 1.5], device=DEV)
+    us = torch.tensor([0.1, 0.5, 0.93], dtype=torch.float64, device=DEV)
+    ops.sample_temperature(logits, temps, us, a, rows=idx)
+    ops.sample_temperature(sub, temps, us, b)
+    assert torch.equal(a, b)
+    got = torch.empty(3, vocab, device=DEV)
+    ops.gather_rows(logits, idx, got)
+    assert torch.equal(got, sub)

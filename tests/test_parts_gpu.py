@@ -316,8 +316,8 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
     w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
     engine = build_engine(folder, dtype=dtype, page_size=4, max_tokens=192, max_slots=3, max_positions=96, shuffle_seed=2)
     # two groups of pages: the windowed entries (0 and 2) and the full ones (3); a state slab for entry 1
-    assert len(engine.cache.groups) == 2 and sorted(len(g.entries) for g in engine.cache.groups) == [1, 2]
-    assert list(engine.cache.states) == [1]
+    assert len(engine.cache.groups) == 2 and sorted(len(g.members) for g in engine.cache.groups) == [1, 2]
+    assert list(engine.cache.states) == [(1, "mixer")]
     g = torch.Generator().manual_seed(3)
     seqs = {r: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for r, n in (("a", 41), ("b", 23))}
     want = {r: toy_plain_forward(cfg, w, t) for r, t in seqs.items()}
@@ -739,3 +739,271 @@ def test_toy_norm_and_block_between_products_that_leave_sums_owed(tmp_path, dtyp
     if dtype == "bfloat16":
         assert owed_made, "no product of this model left its sums to a reader: the sizes are too small for the test"
         assert folds_run, "the toy norm's callers never folded for it"
+
+
+# ---------------------------------------------------------------------------
+# A fourth toy: a block that holds TWO cache-keeping parts under names of its own (an attention
+# over one latent row per position, kept in a cache with a single plane, beside the mixer with
+# fixed-size state), so a layer's cache is a dict by part name and nothing is called "mixer".
+
+def register_latent_toy():
+    from axon_b200.config.base import ModelConfig, register_architecture
+    from axon_b200.kernels import linear as kernels_linear
+    from axon_b200.kernels import ops
+    from axon_b200.parts import KvNeed, LayerSpec, Mixer, ModelSpec, Part, PartSpec, ScheduleEntry, TensorDecl, register_part
+    register_toy()            # the running-mean mixer is defined there
+
+    @register_part
+    class LatentAttention(Mixer):
+        """Every position keeps one latent row ``c = W_c h``; head ``i`` scores its query
+        ``W_q,i h`` against the latents of positions 0..pos and takes their weighted sum:
+        the latent is key and value at once, so the cache has one plane."""
+        category, kind = "mixer", "toy_latent_attention"
+
+        @classmethod
+        def tensors(cls, spec):
+            p = spec.params
+            d, h, r = p["hidden_size"], p["heads"], p["latent"]
+            return {"qc": TensorDecl(((h + 1) * r, d)), "o": TensorDecl((d, h * r))}
+
+        @classmethod
+        def cache_need(cls, spec):
+            return KvNeed(1, int(spec.params["latent"]), planes=1)
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            p = spec.params
+            self.heads, self.r = int(p["heads"]), int(p["latent"])
+            self.w_qc, self.w_o = tensors["qc"], tensors["o"]
+
+        def compute(self, h, ctx, cache):
+            rt, n = self.rt, h.shape[0]
+            assert cache.planes == 1 and cache.v_dim == self.r
+            qc = torch.empty(n, (self.heads + 1) * self.r, dtype=torch.float32, device=h.device)
+            kernels_linear.linear(h, self.w_qc, qc, precise=rt.precise)
+            q = torch.empty(n, self.heads * self.r, dtype=rt.dtype, device=h.device)
+            ops.rope_kv_write(qc, None, ctx.positions, ctx.token_slot, q, cache, self.heads, 0)
+            att = torch.empty_like(q)
+            kernels_linear.attention(q, cache, ctx, att, self.heads, 1.0 / math.sqrt(self.r), precise=rt.precise)
+            out = torch.empty(n, self.w_o.shape[0], dtype=torch.float32, device=h.device)
+            kernels_linear.linear(att, self.w_o, out, precise=rt.precise)
+            return out
+
+    @register_part
+    class TwoMixerBlock(Part):
+        """``x += recall(norm(x)) + memory(norm(x))``: two parts that each keep something."""
+        category, kind = "block", "toy_two_mixers"
+        nested = {"norm": "norm", "recall": "mixer", "memory": "mixer"}
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            self.norm, self.recall, self.memory = (build(spec.parts[k]) for k in ("norm", "recall", "memory"))
+
+        def forward(self, x, ctx, cache, write_cache=True):
+            assert sorted(cache) == ["memory", "recall"]
+            h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            self.norm.forward(x, h)
+            self.recall.forward(h, x, ctx, cache["recall"], write_cache)
+            self.memory.forward(h, x, ctx, cache["memory"], write_cache)
+
+    @dataclass(frozen=True)
+    class LatentToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "LatentToyForCausalLM"
+        model_types: ClassVar[Tuple[str, ...]] = ("latent_toy_test",)
+        width: int = 48
+        words: int = 61
+        heads: int = 3
+        latent: int = 24
+        depth: int = 2
+        eps: float = 1e-5
+        longest: int = 64
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg})
+
+    def latent_spec(c):
+        norm = lambda name: PartSpec("rmsnorm", {"size": c.width, "eps": c.eps}, {"gain": name})
+
+        def layer(i):
+            return LayerSpec("toy_two_mixers", {
+                "norm": norm(f"l{i}.n"),
+                "recall": PartSpec("toy_latent_attention", {"hidden_size": c.width, "heads": c.heads, "latent": c.latent},
+                                   {"qc": f"l{i}.recall.qc", "o": f"l{i}.recall.o"}),
+                "memory": PartSpec("toy_running_mean", {"hidden_size": c.width}, {"w": f"l{i}.memory.w"})})
+        return ModelSpec("LatentToyForCausalLM", c.width, c.words, c.longest,
+                         PartSpec("embedding", {"vocab_size": c.words, "hidden_size": c.width}, {"table": "embed"}),
+                         tuple(layer(i) for i in range(c.depth)), tuple(ScheduleEntry(i) for i in range(c.depth)),
+                         norm("final"),
+                         PartSpec("linear_head", {"vocab_size": c.words, "hidden_size": c.width}, {"weight": "head"}))
+
+    register_architecture(LatentToyConfig, latent_spec)
+    return LatentToyConfig
+
+
+def latent_plain_forward(c, w, tokens):
+    T = len(tokens)
+    x = plain.embed(w["embed"], tokens)
+    for i in range(c.depth):
+        h = plain.rms_norm(x, w[f"l{i}.n"], c.eps)
+        qc = plain.linear(h, w[f"l{i}.recall.qc"])
+        q = qc[:, :c.heads * c.latent].view(T, c.heads, c.latent)
+        lat = qc[:, c.heads * c.latent:].view(T, 1, c.latent)
+        o = plain.causal_gqa_attention(q, lat, lat).reshape(T, c.heads * c.latent)
+        mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+        x = x + plain.linear(o, w[f"l{i}.recall.o"]) + plain.linear(mean, w[f"l{i}.memory.w"])
+    return plain.linear(plain.rms_norm(x, w["final"], c.eps), w["head"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_block_with_two_cache_keeping_parts_and_a_one_plane_cache(tmp_path, dtype):
+    import os
+    import subprocess
+
+    from safetensors.torch import load_file
+
+    from axon_b200.engine.build import build_engine
+    from axon_b200.engine.replay import Replayer
+    from axon_b200.weights import write_random_model
+    cfg = register_latent_toy()()
+    folder = str(tmp_path / "latent")
+    write_random_model(folder, cfg, seed=17, std=0.15)
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    engine = build_engine(folder, dtype=dtype, page_size=8, max_tokens=128, max_slots=2, max_positions=cfg.longest, shuffle_seed=4)
+    # one group of pages with a single plane per position and run; a state slab per run
+    assert len(engine.cache.groups) == 1 and engine.cache.groups[0].need.planes == 1
+    assert engine.cache.groups[0].pool.shape == (17, cfg.depth, 8 * cfg.latent)
+    assert sorted(engine.cache.states) == [(0, "memory"), (1, "memory")]
+    assert engine.cache.parts(0) == ["recall", "memory"] and engine.cache.bytes_per_token() == cfg.depth * cfg.latent * (4 if dtype == "float32" else 2)
+    g = torch.Generator().manual_seed(6)
+    seqs = {r: torch.randint(0, cfg.words, (n,), generator=g).tolist() for r, n in (("a", 39), ("b", 21))}
+    want = {r: latent_plain_forward(cfg, w, t) for r, t in seqs.items()}
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    rp, fed = Replayer(engine), {"a": 0, "b": 0}
+    plan = [[("a", 10)], [("a", 1), ("b", 6)], [("a", 2), ("b", 1)], [("b", 14)], [("a", 26)]]
+    for k, row in enumerate(plan):
+        ents, rows = [], []
+        for r, n in row:
+            t = seqs[r][fed[r]:fed[r] + n]
+            ents.append({"id": r, "tokens": t, "want": list(range(len(t)))})
+            rows += [want[r][fed[r] + j] for j in range(len(t))]
+            fed[r] += len(t)
+        got = rp.run_step({"step": k, "entries": ents, "end": [r for r, _ in row if fed[r] == len(seqs[r])]})
+        close(got, torch.stack(rows), tol, f"latent toy, step {k}")
+    engine.cache.flush()
+    engine.cache.manager.check()
+    assert engine.cache.manager.free_pages(0) == engine.cache.n_pages
+    if dtype == "float32":
+        # `axon info` prints an architecture it has never heard of from its spec and its own keys
+        import io
+        from contextlib import redirect_stdout
+        from axon_b200 import cli
+        buf = io.StringIO()
+        with redirect_stdout(buf):
+            assert cli.cmd_info(folder) == 0
+        text = buf.getvalue()
+        assert "LatentToyForCausalLM" in text and "layers 2 (schedule of 2 runs) / dim 48 / vocab 61 / ctx 64" in text
+        assert "latent 24" in text and "keys of 24 (one plane) x 1 kv heads" in text and "state [49] float32" in text
+        assert "2 x toy_two_mixers(memory: toy_running_mean, norm: rmsnorm, recall: toy_latent_attention)" in text
+        assert "l1.recall.qc -> matrix BF16 [96, 48]" in text
+
+
+# ---------------------------------------------------------------------------
+# A part that calls itself safe for CUDA graphs and is not: the capture fails, the engine keeps
+# such steps eager from then on, and the results are right all the same (the reference injects
+# the failure on the host as well: src/cuda/mod.rs:148-161, src/cuda/qwen2/slots.rs:2629-2700).
+
+def test_a_failed_graph_capture_falls_back_to_eager_steps(tmp_path):
+    from safetensors.torch import load_file
+
+    from axon_b200.config.base import ModelConfig, register_architecture
+    from axon_b200.engine.build import build_engine
+    from axon_b200.engine.step import StepEntry
+    from axon_b200.kernels import linear as kernels_linear
+    from axon_b200.parts import FeedForward, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorDecl, register_part
+    from axon_b200.weights import write_random_model
+
+    @register_part
+    class FragileFeedForward(FeedForward):
+        """``W_out relu(W_in h)``; claims to be safe for graphs but refuses to run inside a capture."""
+        category, kind = "ffn", "toy_fragile_ffn"
+        graph_safe = True
+        captures_refused = 0
+
+        @classmethod
+        def tensors(cls, spec):
+            d, f = spec.params["hidden_size"], spec.params["size"]
+            return {"w_in": TensorDecl((f, d)), "w_out": TensorDecl((d, f))}
+
+        def __init__(self, spec, tensors, rt, build):
+            super().__init__(spec, tensors, rt, build)
+            self.w_in, self.w_out = tensors["w_in"], tensors["w_out"]
+
+        def compute(self, h, ctx):
+            if torch.cuda.is_current_stream_capturing():
+                FragileFeedForward.captures_refused += 1
+                raise RuntimeError("this part cannot be captured")
+            mid = self.rt.buffer("fragile_mid", (h.shape[0], self.w_in.shape[0]))
+            kernels_linear.linear(h, self.w_in, mid, precise=self.rt.precise)
+            out = self.rt.buffer("fragile_out", (h.shape[0], self.w_out.shape[0]), torch.float32)
+            kernels_linear.linear(mid.clamp_(min=0), self.w_out, out, precise=self.rt.precise)
+            return out
+
+    @dataclass(frozen=True)
+    class FragileConfig(ModelConfig):
+        architecture: ClassVar[str] = "FragileToyForCausalLM"
+        model_types: ClassVar[Tuple[str, ...]] = ("fragile_toy_test",)
+        hidden_size: int = 64
+        vocab_size: int = 90
+        size: int = 80
+        eps: float = 1e-5
+
+        @classmethod
+        def from_dict(cls, cfg):
+            return cls(**{k: cfg[k] for k in cls.__dataclass_fields__ if k in cfg})
+
+    def spec_of(c):
+        norm = lambda name: PartSpec("rmsnorm", {"size": c.hidden_size, "eps": c.eps}, {"gain": name})
+        attn = PartSpec("attention", {"hidden_size": c.hidden_size, "heads": 4, "kv_heads": 2, "head_dim": 16,
+                                      "qkv_bias": False, "out_bias": False, "window": None, "scale": None},
+                        {k: f"attn.{k}" for k in ("q", "k", "v", "o")},
+                        {"position": PartSpec("rope", {"head_dim": 16, "theta": 1e4, "pairing": "half"})})
+        ffn = PartSpec("toy_fragile_ffn", {"hidden_size": c.hidden_size, "size": c.size}, {"w_in": "ffn.in", "w_out": "ffn.out"})
+        layer = LayerSpec("prenorm", {"norm_mixer": norm("n1"), "mixer": attn, "norm_ffn": norm("n2"), "ffn": ffn})
+        return ModelSpec("FragileToyForCausalLM", c.hidden_size, c.vocab_size, 64,
+                         PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"table": "embed"}),
+                         (layer,), (ScheduleEntry(0),), norm("final"),
+                         PartSpec("linear_head", {"vocab_size": c.vocab_size, "hidden_size": c.hidden_size}, {"weight": "head"}))
+
+    register_architecture(FragileConfig, spec_of)
+    c = FragileConfig()
+    folder = str(tmp_path / "fragile")
+    write_random_model(folder, c, seed=2, std=0.2)
+    w = {k: v.double() for k, v in load_file(folder + "/model.safetensors").items()}
+    toks = torch.randint(0, c.vocab_size, (30,), generator=torch.Generator().manual_seed(1)).tolist()
+    T = len(toks)
+    x = plain.embed(w["embed"], toks)
+    h = plain.rms_norm(x, w["n1"], c.eps)
+    q, k, v = (plain.linear(h, w[f"attn.{n}"]).view(T, heads, 16) for n, heads in (("q", 4), ("k", 2), ("v", 2)))
+    pos = list(range(T))
+    o = plain.causal_gqa_attention(plain.rope_half(q, pos, 1e4), plain.rope_half(k, pos, 1e4), v).reshape(T, 64)
+    x = x + plain.linear(o, w["attn.o"])
+    h = plain.rms_norm(x, w["n2"], c.eps)
+    x = x + plain.linear(torch.relu(plain.linear(h, w["ffn.in"])), w["ffn.out"])
+    want = plain.linear(plain.rms_norm(x, w["final"], c.eps), w["head"])
+
+    for dtype in ("bfloat16", "float32"):
+        FragileFeedForward.captures_refused = 0
+        engine = build_engine(folder, dtype=dtype, page_size=16, max_tokens=64, max_slots=2, max_positions=64)
+        assert engine.cuda_graphs, "every part says it is safe: the engine will try to capture"
+        s = engine.open_request()
+        got = [engine.step([StepEntry(s, toks[:20], [19])]).double().cpu()]
+        for t in range(20, T):
+            got.append(engine.step([StepEntry(s, [toks[t]], [0])]).double().cpu())
+        assert FragileFeedForward.captures_refused == 1, "one capture was tried and failed"
+        assert not engine.cuda_graphs and not engine._graphs, "steps of single tokens stay eager after the failure"
+        close(torch.cat(got), want[19:], TOL[torch.float32 if dtype == "float32" else torch.bfloat16], f"{dtype}, after a failed capture")
+        # the engine still steps: another request, fed in portions (a portion's capture fails too and is given up)
+        s2 = engine.open_request()
+        rows = [engine.step([StepEntry(s2, toks[a:a + 5], [4])]).double().cpu() for a in (0, 5, 10)]
+        close(torch.cat(rows), want[[4, 9, 14]], TOL[torch.float32 if dtype == "float32" else torch.bfloat16], f"{dtype}, portions")

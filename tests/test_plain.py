@@ -118,6 +118,56 @@ def test_mutations_move_the_logits(models):
 
 
 def test_greedy_takes_the_last_of_equal_maxima(models):
+    """A tie is built: two rows of the (untied) head are made equal and their gain so large that
+    they are the two largest logits at every place; the larger id must be picked
+    (src/generate.rs:222-263)."""
     cfg, w = models["B"]
-    out = plain.greedy(cfg, w, [1, 2, 3], 4)
-    assert len(out) == 4 and all(0 <= t < cfg["vocab_size"] for t in out)
+    w = dict(w)
+    head = w["lm_head.weight"].clone()
+    lo, hi = 17, 301
+    ids = [1, 2, 3]
+    # the planted rows are multiples of the normed state that reaches the head at the last place,
+    # which a first run records
+    state = {}
+    orig = plain.linear
+
+    def spy(x, wt, b=None):
+        if wt is head_now[0]:
+            state["h"] = x.clone()
+        return orig(x, wt, b)
+    head_now = [head]
+    plain.linear = spy
+    try:
+        w["lm_head.weight"] = head
+        plain.forward(cfg, w, ids)
+    finally:
+        plain.linear = orig
+    h = state["h"][-1]
+    head[lo] = head[hi] = 50.0 * h / (h @ h)           # both logits exactly 50 at the last place
+    w["lm_head.weight"] = head
+    row = plain.forward(cfg, w, ids)[-1]
+    assert row[lo] == row[hi] == row.max(), "the two planted rows must tie for the maximum"
+    assert plain.greedy(cfg, w, ids, 1) == [hi]
+    # and with the rows swapped in value the smaller id still loses: the rule is "last index"
+    head[hi] = head[hi] * 0.5
+    w["lm_head.weight"] = head
+    assert plain.greedy(cfg, w, ids, 1) == [lo]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_two_plain_implementations_agree(model_folders, models, name):
+    """The torch implementation (whole sequences, masked matrices) and the numpy one (token by
+    token, explicit loops, its own file reader) were written separately from the same formulas;
+    they must agree to rounding of float64."""
+    import numpy as np
+    import plain_loops
+    cfg, w = models[name]
+    cfg2, w2 = plain_loops.read_folder(model_folders[name])
+    assert cfg2 == cfg
+    for k, v in w.items():
+        assert np.array_equal(v.numpy(), w2[k]), f"the two readers differ on {k}"
+    ids = _tokens(cfg, 19, 77)
+    a = plain.forward(cfg, w, ids).numpy()
+    b = plain_loops.forward(cfg2, w2, ids)
+    assert a.shape == b.shape
+    assert float(np.abs(a - b).max()) <= 1e-10 * max(1.0, float(np.abs(a).max()))
