@@ -74,6 +74,9 @@ class Engine:
         self._graph_generation = self.rt.generation
         #: steps run, for reports
         self.steps = 0
+        # the metadata buffer of eager steps at its largest from the start: a buffer that grows later
+        # moves, and every captured graph is dropped when any scratch buffer moves
+        self.rt.buffer("step_meta", (4 * max_step_tokens + 6 * cache.max_slots,), torch.int32)
 
     # -- requests ---------------------------------------------------------
     def open_request(self) -> int:
