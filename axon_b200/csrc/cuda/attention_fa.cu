@@ -133,12 +133,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // copies one 16-byte chunk of every RPP-th row.  When the page size divides 64 a row's page within
 // the tile and its place inside that page are the same for every tile, so they are worked out once
 // (the division by the page size per row and tile was a third of the decode kernel's instructions).
-template <int HD> struct KvLoader {
+template <int HD, bool CHECKED> struct KvLoader {
     static constexpr int CPR = HD / 8, RPP = FA_THREADS / CPR, ITER = FA_BN / RPP;
     const int32_t* bt;              // the request's row of the block table
     const __nv_bfloat16* src0;      // this thread's chunk of row 0 of the kv head in page 0 (K plane)
     long long page_stride, v_off;
-    PagedKv kvc;                    // for checked tables
+    unsigned int* fault;            // checked tables (see kv_layout.h): null when off
+    int n_pages;
     int ps, pages_per_tile, last_page, kv_len, r0;
     int in_page[ITER], page_of[ITER];
     uint32_t dst[ITER];
@@ -146,7 +147,7 @@ template <int HD> struct KvLoader {
     __device__ __forceinline__ void init(const __nv_bfloat16* pool, const PagedKv& kv, int slot, int kvh, int kv_len_) {
         const int c = threadIdx.x % CPR;
         r0 = threadIdx.x / CPR;
-        ps = kv.page_size; kv_len = kv_len_; kvc = kv;
+        ps = kv.page_size; kv_len = kv_len_; fault = kv.fault; n_pages = kv.n_pages;
         bt = kv.block_table + (long long)slot * kv.table_stride;
         src0 = pool + kv.entry_offset + (long long)kvh * ps * HD + c * 8;
         page_stride = kv.page_stride; v_off = kv.v_offset;
@@ -160,22 +161,41 @@ template <int HD> struct KvLoader {
             dst[j] = Swz<HD>::off(r, c);
         }
     }
+    __device__ __forceinline__ int checked(int entry) const {
+        if ((unsigned)entry > (unsigned)n_pages) { fault[1] = (unsigned)entry; fault[0] = 1u; return n_pages; }
+        return entry;
+    }
     // rows past the request's length read its last page (fast path) or last position: finite data, masked later
     __device__ __forceinline__ void load(uint32_t k_tile, uint32_t v_tile, int key0) const {
         if (pages_per_tile) {
             const int first = (key0 / FA_BN) * pages_per_tile;
+            // every table entry is loaded before any is checked: a check may store (the fault
+            // record), and loads behind a possible store are not issued together
+            int page[ITER];
+#pragma unroll
+            for (int j = 0; j < ITER; ++j) page[j] = bt[min(first + page_of[j], last_page)];
+            if (CHECKED) {
+#pragma unroll
+                for (int j = 0; j < ITER; ++j) page[j] = checked(page[j]);
+            }
 #pragma unroll
             for (int j = 0; j < ITER; ++j) {
-                const int page = kvc.page(bt[min(first + page_of[j], last_page)]);
-                const __nv_bfloat16* src = src0 + (long long)page * page_stride + in_page[j];
+                const __nv_bfloat16* src = src0 + (long long)page[j] * page_stride + in_page[j];
                 cp_async16(k_tile + dst[j], src);
                 cp_async16(v_tile + dst[j], src + v_off);
             }
         } else {
+            int page[ITER];
+#pragma unroll
+            for (int j = 0; j < ITER; ++j) page[j] = bt[min(key0 + r0 + RPP * j, kv_len - 1) / ps];
+            if (CHECKED) {
+#pragma unroll
+                for (int j = 0; j < ITER; ++j) page[j] = checked(page[j]);
+            }
 #pragma unroll
             for (int j = 0; j < ITER; ++j) {
                 const int pos = min(key0 + r0 + RPP * j, kv_len - 1), lp = pos / ps;
-                const __nv_bfloat16* src = src0 + (long long)kvc.page(bt[lp]) * page_stride + (pos - lp * ps) * HD;
+                const __nv_bfloat16* src = src0 + (long long)page[j] * page_stride + (pos - lp * ps) * HD;
                 cp_async16(k_tile + dst[j], src);
                 cp_async16(v_tile + dst[j], src + v_off);
             }
@@ -186,7 +206,11 @@ template <int N> __device__ __forceinline__ void cp_async_wait_pending() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int HD, bool DECODE>
+// CHECKED: the variant for checked tables (kv_layout.h), a debugging mode.  It is a kernel of its
+// own because a check may store: behind a possible store the compiler does not issue the loads
+// that follow together, which cost the decode shape 2 us a layer at 7B sizes when the check was
+// a run-time branch of the one kernel.
+template <int HD, bool DECODE, bool CHECKED>
 __global__ void __launch_bounds__(FA_THREADS, (DECODE || HD == 128) ? 2 : 3)   // as many CTAs as shared memory holds
 attention_fa_kernel(const FaParams p) {
     constexpr int BM = DECODE ? 16 : 64;
@@ -227,7 +251,7 @@ attention_fa_kernel(const FaParams p) {
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi, t_begin + per);
 
     const int new_from = kv_len - q_len;              // the segment's first position written by this step
-    KvLoader<HD> loader;
+    KvLoader<HD, CHECKED> loader;
     loader.init(p.pool, p.kv, slot, kvh, kv_len);
     if (DECODE) {
 #pragma unroll
@@ -252,7 +276,8 @@ attention_fa_kernel(const FaParams p) {
                 if (pos0 + j < t_begin * FA_BN || pos0 + j >= t_end * FA_BN) continue;
                 float4 ra, rb;
                 rotated_quads(p, q_start + tok0 + j, q_dim + (is_v ? kv_dim : 0) + kvh * HD, HALF, i0, !is_v, ra, rb);
-                __nv_bfloat16* dst = p.pool_rw + p.kv.row(slot, pos0 + j, kvh) + (is_v ? p.kv.v_offset : 0);
+                __nv_bfloat16* dst = p.pool_rw + (CHECKED ? p.kv.row(slot, pos0 + j, kvh) : p.kv.row_unchecked(slot, pos0 + j, kvh)) +
+                                     (is_v ? p.kv.v_offset : 0);
                 *reinterpret_cast<uint2*>(dst + i0) = make_uint2(pack_bf16(ra.x, ra.y), pack_bf16(ra.z, ra.w));
                 *reinterpret_cast<uint2*>(dst + HALF + i0) = make_uint2(pack_bf16(rb.x, rb.y), pack_bf16(rb.z, rb.w));
             }
@@ -629,15 +654,15 @@ __global__ void __launch_bounds__(FA_COMBINE_THREADS) attention_combine_kernel(c
     }
 }
 
-template <int HD, bool DECODE>
+template <int HD, bool DECODE, bool CHECKED>
 static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t stream) {
     constexpr int BM = DECODE ? 16 : 64;
     constexpr size_t tiles = (DECODE ? (size_t)BM * HD * 2 : 0) + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
     constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
     constexpr size_t smem = tiles > merge ? tiles : merge;
-    if (int st = ensure_dynamic_smem<attention_fa_kernel<HD, DECODE>>(smem, "axon_attention_fa")) return st;
+    if (int st = ensure_dynamic_smem<attention_fa_kernel<HD, DECODE, CHECKED>>(smem, "axon_attention_fa")) return st;
     dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);
-    launch_pdl(attention_fa_kernel<HD, DECODE>, grid, dim3(FA_THREADS), smem, stream, p);
+    launch_pdl(attention_fa_kernel<HD, DECODE, CHECKED>, grid, dim3(FA_THREADS), smem, stream, p);
     int st = launch_status("axon_attention_fa");
     if (st != AXON_OK) return st;
     if (DECODE && p.n_splits > 1 && p.counters == nullptr) {
@@ -697,7 +722,10 @@ static int attention_fa_launch(const void* q, const void* pool, void* out, const
     p.qkv = fused.qkv; p.fold = fused.fold; p.table = fused.table; p.pool_rw = (__nv_bfloat16*)const_cast<void*>(pool);
     p.qkv_width = fused.qkv_width; p.write_kv = fused.write_kv;
 #define AXON_FA_CASE(HD)                                                                         \
-    case HD: return decode ? launch_fa<HD, true>(p, n_items, kvh, stream) : launch_fa<HD, false>(p, n_items, kvh, stream);
+    case HD:                                                                                     \
+        if (p.kv.fault != nullptr)                                                               \
+            return decode ? launch_fa<HD, true, true>(p, n_items, kvh, stream) : launch_fa<HD, false, true>(p, n_items, kvh, stream); \
+        return decode ? launch_fa<HD, true, false>(p, n_items, kvh, stream) : launch_fa<HD, false, false>(p, n_items, kvh, stream);
     switch (hd) {
         AXON_FA_CASE(16)
         AXON_FA_CASE(32)

@@ -51,14 +51,21 @@ struct AtRowMap {
     int pages_per_tile; // 64 / page size, or 0 when the page size does not divide 64
     int last_page;      // logical page of the last key
 };
+template <bool CHECKED>
 __device__ __forceinline__ void at_pages(int (&pg)[8], const AtRowMap& map, const PagedKv& kv, const int32_t* bt, int key0, int kv_len) {
     if (map.pages_per_tile) {
         const int first = (key0 / AT_BN) * map.pages_per_tile;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pg[j] = kv.page(bt[min(first + map.page_of[j], map.last_page)]);   // past the end: finite data, masked later
+        for (int j = 0; j < 8; ++j) pg[j] = bt[min(first + map.page_of[j], map.last_page)];   // past the end: finite data, masked later
     } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pg[j] = kv.page(bt[min(key0 + (int)(threadIdx.x >> 4) + 8 * j, kv_len - 1) / kv.page_size]);
+        for (int j = 0; j < 8; ++j) pg[j] = bt[min(key0 + (int)(threadIdx.x >> 4) + 8 * j, kv_len - 1) / kv.page_size];
+    }
+    // checked tables (a kernel variant of its own, see kv_layout.h): after all eight loads, so
+    // that these stay in flight together
+    if (CHECKED) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pg[j] = kv.page(pg[j]);
     }
 }
 // One 64-key tile of K or V: two 8 KiB halves [dims 0..63 | 64..127][key][64 dims].  `src` points at
@@ -83,6 +90,7 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+template <bool CHECKED>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tc_kernel(const AtParams p) {
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -150,15 +158,15 @@ attention_tc_kernel(const AtParams p) {
     const __nv_bfloat16* k_src = p.pool + p.kv.entry_offset + (long long)kvh * p.kv.page_size * AT_HD + chunk * 8;
     const __nv_bfloat16* v_src = k_src + p.kv.v_offset;
     const uint32_t k_dst = k_sm + dst_off, v_dst = v_sm + dst_off;
-    at_pages(pg_v, map, p.kv, bt, key_base, kv_len);
-    at_pages(pg_k, map, p.kv, bt, key_base + AT_BN, kv_len);
+    at_pages<CHECKED>(pg_v, map, p.kv, bt, key_base, kv_len);
+    at_pages<CHECKED>(pg_k, map, p.kv, bt, key_base + AT_BN, kv_len);
     at_load_tile(k_dst, k_src, map, p.kv, pg_v, key_base, kv_len);
     at_load_tile(v_dst, v_src, map, p.kv, pg_v, key_base, kv_len);
     if (n_tiles > 1) at_load_tile(k_dst + KV_BYTES, k_src, map, p.kv, pg_k, key_base + AT_BN, kv_len);
     asm volatile("cp.async.commit_group;");
 #pragma unroll
     for (int j = 0; j < 8; ++j) pg_v[j] = pg_k[j];
-    at_pages(pg_k, map, p.kv, bt, key_base + 2 * AT_BN, kv_len);
+    at_pages<CHECKED>(pg_k, map, p.kv, bt, key_base + 2 * AT_BN, kv_len);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     fence_async_proxy();                         // what cp.async and st.shared wrote must be seen by the MMA
     tc_fence_before();
@@ -198,7 +206,7 @@ attention_tc_kernel(const AtParams p) {
         asm volatile("cp.async.commit_group;");
 #pragma unroll
         for (int j = 0; j < 8; ++j) pg_v[j] = pg_k[j];
-        at_pages(pg_k, map, p.kv, bt, key0 + 3 * AT_BN, kv_len);         // used in the next round
+        at_pages<CHECKED>(pg_k, map, p.kv, bt, key0 + 3 * AT_BN, kv_len);         // used in the next round
 
         // ---- this row's 64 scores
         uint32_t sr[2][32];
@@ -338,8 +346,13 @@ AXON_API int axon_attention_tc(const void* q, const void* pool, void* out, const
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     constexpr size_t smem = 2 * AT_BM * 128 + 4 * (2 * AT_BN * 128) + AT_BM * 128 + 64;
-    if (int st = ensure_dynamic_smem<attention_tc_kernel>(smem, "axon_attention_tc")) return st;
-    attention_tc_kernel<<<dim3(n_items, kvh), AT_THREADS, smem, stream>>>(p);
+    if (p.kv.fault != nullptr) {
+        if (int st = ensure_dynamic_smem<attention_tc_kernel<true>>(smem, "axon_attention_tc")) return st;
+        attention_tc_kernel<true><<<dim3(n_items, kvh), AT_THREADS, smem, stream>>>(p);
+    } else {
+        if (int st = ensure_dynamic_smem<attention_tc_kernel<false>>(smem, "axon_attention_tc")) return st;
+        attention_tc_kernel<false><<<dim3(n_items, kvh), AT_THREADS, smem, stream>>>(p);
+    }
     return launch_status("axon_attention_tc");
 }
 

@@ -150,6 +150,14 @@ struct PagedKv {
         return (long long)pg * page_stride + entry_offset +
                ((long long)kv_head * page_size + (pos - lp * page_size)) * head_dim;
     }
+    // the same without the check, for kernels that have a variant of their own for checked tables
+    // (a check may store, and a possible store keeps the compiler from issuing loads together)
+    __device__ __forceinline__ long long row_unchecked(int slot, int pos, int kv_head) const {
+        const int lp = pos / page_size;
+        const int pg = block_table[(long long)slot * table_stride + lp];
+        return (long long)pg * page_stride + entry_offset +
+               ((long long)kv_head * page_size + (pos - lp * page_size)) * head_dim;
+    }
     // the value row of the same position (from the pool's start, v_offset included)
     __device__ __forceinline__ long long v_row(int slot, int pos, int kv_head) const {
         const int lp = pos / page_size;

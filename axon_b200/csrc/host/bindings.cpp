@@ -83,6 +83,28 @@ PYBIND11_MODULE(axon_host, m) {
             return py::make_tuple(rc, bad);
         })
         .def("commit_decode", [](CacheManager& c, const std::vector<int>& slots) { c.commit_decode(slots.data(), (int)slots.size()); })
+        // any step laid out in one call; see cache_manager.h.  Returns (status, failing entry, tokens,
+        // entries, wanted places, 1 when every entry brings one token, values written to `out`).
+        .def("stage_step", [](CacheManager& c, py::array_t<int32_t, py::array::c_style | py::array::forcecast> slots,
+                              py::array_t<int32_t, py::array::c_style | py::array::forcecast> tok_off,
+                              py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens,
+                              py::array_t<int32_t, py::array::c_style | py::array::forcecast> want_off,
+                              py::array_t<int32_t, py::array::c_style | py::array::forcecast> wants, int vocab,
+                              int max_step_tokens, py::array_t<int32_t, py::array::c_style> out) {
+            const int n = (int)slots.size();
+            if (tok_off.size() != n + 1 || want_off.size() != n + 1) throw CacheError("stage_step: offsets need one value more than there are entries");
+            if (n > 0 && (tokens.size() < tok_off.data()[n] || wants.size() < want_off.data()[n]))
+                throw CacheError("stage_step: offsets reach past the token or wanted-place lists");
+            CacheManager::StepLayout lay;
+            int bad = -1;
+            const int rc = c.stage_step(slots.data(), tok_off.data(), tokens.data(), want_off.data(), wants.data(), n, vocab,
+                                        max_step_tokens, out.mutable_data(), (long long)out.size(), &lay, &bad);
+            return py::make_tuple(rc, bad, lay.n_tokens, lay.n_entries, lay.n_want, lay.decode_only, lay.total);
+        })
+        .def("commit_step", [](CacheManager& c, py::array_t<int32_t, py::array::c_style | py::array::forcecast> segments, int n) {
+            if (segments.size() < 4 * (py::ssize_t)n) throw CacheError("commit_step: segments are [4][entries]");
+            c.commit_step(segments.data(), n);
+        })
         // the host block table of a group as a numpy view [max_slots][stride] (no copy)
         .def("table", [](CacheManager& c, int g) {
             return py::array_t<int32_t>({(py::ssize_t)c.max_slots(), (py::ssize_t)c.table_stride(g)},
@@ -172,7 +194,32 @@ PYBIND11_MODULE(axon_host, m) {
     py::class_<Plan>(m, "Plan")
         .def_readonly("entries", &Plan::entries)
         .def_readonly("preempted", &Plan::preempted)
-        .def_readonly("n_tokens", &Plan::n_tokens);
+        .def_readonly("n_tokens", &Plan::n_tokens)
+        .def_property_readonly("n_entries", [](const Plan& p) { return (int)p.entries.size(); })
+        // The plan as arrays, for the step function's native staging: request ids and slots of the
+        // entries, token offsets (entries + 1) and the tokens, offsets of wanted places (entries + 1)
+        // and the places (the last token of an entry that wants logits).
+        .def("flat", [](const Plan& p) {
+            const py::ssize_t n = (py::ssize_t)p.entries.size();
+            py::array_t<int64_t> ids(n);
+            py::ssize_t n_want = 0, n_tok = 0;
+            for (const PlanEntry& e : p.entries) { n_want += e.want_logits ? 1 : 0; n_tok += (py::ssize_t)e.tokens.size(); }
+            py::array_t<int32_t> slots(n), tok_off(n + 1), want_off(n + 1), tokens(n_tok);
+            py::array_t<int32_t> wants(n_want);
+            int64_t* idp = ids.mutable_data();
+            int32_t *sp = slots.mutable_data(), *to = tok_off.mutable_data(), *wo = want_off.mutable_data();
+            int32_t *tp = tokens.mutable_data(), *wp = wants.mutable_data();
+            int at = 0, w = 0;
+            to[0] = wo[0] = 0;
+            for (py::ssize_t i = 0; i < n; ++i) {
+                const PlanEntry& e = p.entries[(size_t)i];
+                idp[i] = e.id; sp[i] = e.slot;
+                for (int32_t t : e.tokens) tp[at++] = t;
+                if (e.want_logits) wp[w++] = (int32_t)e.tokens.size() - 1;
+                to[i + 1] = at; wo[i + 1] = w;
+            }
+            return py::make_tuple(ids, slots, tok_off, tokens, want_off, wants);
+        });
 
     py::class_<Done>(m, "Done").def_readonly("id", &Done::id).def_readonly("finish", &Done::finish);
 
@@ -184,6 +231,9 @@ PYBIND11_MODULE(axon_host, m) {
         .def("abort", &Scheduler::abort)
         .def("plan", &Scheduler::plan)
         .def("commit", &Scheduler::commit)
+        .def("commit_in_order", [](Scheduler& s, const Plan& plan, py::array_t<int32_t, py::array::c_style | py::array::forcecast> picks) {
+            return s.commit_in_order(plan, picks.data(), (int)picks.size());
+        })
         .def("idle", &Scheduler::idle)
         .def("request", &Scheduler::request, py::return_value_policy::copy)
         .def("take_output", &Scheduler::take_output)

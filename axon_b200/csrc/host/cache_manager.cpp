@@ -250,6 +250,58 @@ void CacheManager::commit_decode(const int* slots, int n) {
     for (int i = 0; i < n; ++i) commit(slots[i], slots_[slots[i]].length + 1);
 }
 
+int CacheManager::stage_step(const int* slots, const int* tok_off, const int32_t* tokens, const int* want_off,
+                             const int* wants, int n_entries, int vocab, int max_step_tokens, int32_t* out,
+                             long long out_capacity, StepLayout* lay, int* bad) {
+    *bad = -1;
+    if (n_entries <= 0) return 1;
+    const int S = n_entries;
+    if (tok_off[0] != 0 || want_off[0] != 0) return 1;
+    const long long T = tok_off[S], W = want_off[S];
+    if (T > max_step_tokens) return 1;
+    stage_seen_.assign((size_t)max_slots_, 0);
+    bool decode_only = true;
+    for (int i = 0; i < S; ++i) {
+        const int s = slots[i];
+        if (s < 0 || s >= max_slots_ || !is_open(s) || stage_seen_[s]) return 1;
+        stage_seen_[s] = 1;
+        const int k = tok_off[i + 1] - tok_off[i];
+        if (k <= 0 || want_off[i + 1] < want_off[i]) return 1;
+        if (k != 1) decode_only = false;
+        for (int t = tok_off[i]; t < tok_off[i + 1]; ++t)
+            if (tokens[t] < 0 || tokens[t] >= vocab) return 1;
+        for (int w = want_off[i]; w < want_off[i + 1]; ++w)
+            if (wants[w] < 0 || wants[w] >= k) return 1;
+        if ((long long)slots_[s].length + k > max_positions_) return 1;
+    }
+    const long long total = 3 * T + 4 * S + W + (decode_only ? 2 * S : 0);
+    if (total > out_capacity) return 1;
+    flush();
+    for (int i = 0; i < S; ++i) {
+        if (!reserve(slots[i], slots_[slots[i]].length + (tok_off[i + 1] - tok_off[i]))) { *bad = i; return 2; }
+    }
+    int32_t* tok = out; int32_t* pos = out + T; int32_t* sl = out + 2 * T; int32_t* seg = out + 3 * T;
+    int32_t* want = seg + 4 * S;
+    int n_want = 0;
+    for (int i = 0; i < S; ++i) {
+        const int at = tok_off[i], k = tok_off[i + 1] - at, start = slots_[slots[i]].length;
+        for (int j = 0; j < k; ++j) { tok[at + j] = tokens[at + j]; pos[at + j] = start + j; sl[at + j] = slots[i]; }
+        seg[i] = slots[i]; seg[S + i] = at; seg[2 * S + i] = k; seg[3 * S + i] = start + k;
+        for (int w = want_off[i]; w < want_off[i + 1]; ++w) want[n_want++] = at + wants[w];
+    }
+    if (decode_only) {
+        int32_t* items = want + n_want;
+        for (int i = 0; i < S; ++i) { items[2 * i] = i; items[2 * i + 1] = 0; }
+    }
+    lay->n_tokens = (int)T; lay->n_entries = S; lay->n_want = n_want; lay->decode_only = decode_only ? 1 : 0;
+    lay->total = (int)total;
+    return 0;
+}
+
+void CacheManager::commit_step(const int32_t* segments, int n_entries) {
+    for (int i = 0; i < n_entries; ++i) commit(segments[i], segments[3 * n_entries + i]);
+}
+
 int CacheManager::slot_pages(int g, int slot) const {
     if (!is_open(slot)) return 0;
     const Slot& sl = slots_[slot];

@@ -98,6 +98,21 @@ public:
     // The lengths of those requests grow by one.
     void commit_decode(const int* slots, int n);
 
+    // Any step, laid out for the device in one call: entry i brings tokens[tok_off[i] .. tok_off[i+1])
+    // for the request in slots[i] and wants the logits at the places wants[want_off[i] .. want_off[i+1])
+    // among them.  Checks as stage_decode (and that a step holds at most max_step_tokens tokens and
+    // every wanted place lies inside its entry), flushes, takes the pages, and fills `out`:
+    //   tokens[T] positions[T] slots[T] segments[4][S] (slot, q_start, q_len, kv_len) wanted rows[W]
+    //   and, when every entry brings one token, items[S][2] (segment, 0)
+    // with T tokens, S entries and W wanted places in all (`lay`).  `out` must hold
+    // 3 T + 6 S + W values.  Returns as stage_decode.
+    struct StepLayout { int n_tokens = 0, n_entries = 0, n_want = 0, decode_only = 0, total = 0; };
+    int stage_step(const int* slots, const int* tok_off, const int32_t* tokens, const int* want_off, const int* wants,
+                   int n_entries, int vocab, int max_step_tokens, int32_t* out, long long out_capacity,
+                   StepLayout* lay, int* bad);
+    // The lengths of the step's requests grow by what the step brought (`segments` as laid out above).
+    void commit_step(const int32_t* segments, int n_entries);
+
     int free_pages(int g) const { return allocs_.at(g).n_free(); }
     int retired_pages(int g) const { return allocs_.at(g).n_retired(); }
     int held_pages(int g) const { return allocs_.at(g).n_held(); }

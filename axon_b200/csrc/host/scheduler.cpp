@@ -130,6 +130,8 @@ Plan Scheduler::plan() {
         p.entries.erase(std::remove_if(p.entries.begin(), p.entries.end(),
                                        [&](const PlanEntry& e) { return requests_.at(e.id).slot != e.slot; }),
                         p.entries.end());
+        p.n_tokens = 0;
+        for (const PlanEntry& e : p.entries) p.n_tokens += (int)e.tokens.size();
 
         auto feed = [&](Request& r) {
             const int remaining = (int)r.tokens.size() - r.fed;
@@ -227,6 +229,18 @@ std::vector<Done> Scheduler::commit(const Plan& plan, const std::map<int64_t, in
         }
     }
     return done;
+}
+
+std::vector<Done> Scheduler::commit_in_order(const Plan& plan, const int32_t* picks, int n_picks) {
+    std::map<int64_t, int32_t> picked;
+    int k = 0;
+    for (const PlanEntry& e : plan.entries) {
+        if (!e.want_logits) continue;
+        if (k >= n_picks) throw SchedulerError("fewer tokens were reported than the plan's entries wanted");
+        picked[e.id] = picks[k++];
+    }
+    if (k != n_picks) throw SchedulerError("more tokens were reported than the plan's entries wanted");
+    return commit(plan, picked);
 }
 
 std::vector<int32_t> Scheduler::take_output(int64_t id) {

@@ -80,6 +80,8 @@ public:
     Plan plan();
     // `picked`: for every entry of the plan that wanted logits, the token chosen from them.
     std::vector<Done> commit(const Plan& plan, const std::map<int64_t, int32_t>& picked);
+    // The same with the picks in the order of the plan's entries that wanted logits.
+    std::vector<Done> commit_in_order(const Plan& plan, const int32_t* picks, int n_picks);
 
     bool idle() const;  // nothing waiting, nothing running
     int n_waiting() const { return (int)waiting_.size(); }

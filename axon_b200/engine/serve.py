@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..kernels import lib
@@ -31,6 +32,8 @@ class BatchRunner:
         self.finish: Dict[int, str] = {}
         self.preemptions = 0
         self.steps = 0
+        #: tokens run over all steps (prompt portions and decoded tokens), for reports
+        self.step_tokens = 0
 
     def add(self, rid: int, prompt: Sequence[int], n_gen: int, stop: Sequence[int] = (),
             sample: Optional[SampleCfg] = None) -> None:
@@ -42,26 +45,32 @@ class BatchRunner:
         self.samplers[int(rid)] = RowSampler(sample, prompt)
 
     def step(self, on_token: Optional[Callable[[int, int], None]] = None) -> List[int]:
-        """One scheduler iteration; the ids of requests that finished in it."""
+        """One scheduler iteration; the ids of requests that finished in it.  The plan goes to the
+        step function as arrays (no Python object per entry or token); when every row that wants
+        a token is greedy, the pick is part of the step (of its CUDA graph) and one small copy
+        brings the ids back."""
         plan = self.sched.plan()
         self.preemptions += len(plan.preempted)
-        entries, wanted = [], []
-        for e in plan.entries:
-            entries.append(StepEntry(e.slot, e.tokens, [len(e.tokens) - 1] if e.want_logits else []))
-            if e.want_logits:
-                wanted.append(e.id)
-        logits = self.engine.step(entries)
-        picked: Dict[int, int] = {}
-        if wanted:
-            toks = pick_tokens(logits, [self.samplers[r] for r in wanted])
-            picked = dict(zip(wanted, toks))
-        done = self.sched.commit(plan, picked)
+        ids, slots, tok_off, tokens, want_off, wants = plan.flat()
+        wanted = ids[np.diff(want_off) > 0].tolist()
+        self.step_tokens += int(tok_off[-1])
+        all_greedy = all(self.samplers[r].greedy for r in wanted)
+        out = self.engine.step_flat(slots, tok_off, tokens, want_off, wants, greedy=all_greedy and bool(wanted))
+        if not wanted:
+            toks = []
+        elif all_greedy:
+            toks = out.tolist()
+            for r, t in zip(wanted, toks):
+                self.samplers[r].history.append(t)
+        else:
+            toks = pick_tokens(out, [self.samplers[r] for r in wanted])
+        done = self.sched.commit_in_order(plan, np.asarray(toks, dtype=np.int32))
         self.steps += 1
         finished = []
-        done_ids = {d.id: d.finish for d in done}
         if on_token is not None:
-            for rid, tok in picked.items():
-                if not (rid in done_ids and done_ids[rid] == lib.host().Finish.Stop):
+            stopped = {d.id for d in done if d.finish == lib.host().Finish.Stop}
+            for rid, tok in zip(wanted, toks):
+                if rid not in stopped:
                     on_token(rid, tok)
         if done:
             self.engine.check_device()      # before a request's tokens are handed out as good

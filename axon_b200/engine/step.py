@@ -15,6 +15,7 @@ runs, as ``StepError::Input`` does (src/cuda/qwen2/slots.rs:393-438).
 
 from __future__ import annotations
 
+from collections.abc import Sequence as SequenceABC
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -48,6 +49,31 @@ class StepEntry:
     tokens: Sequence[int]
     #: places among ``tokens`` whose logits are wanted
     want: Sequence[int] = field(default_factory=tuple)
+
+
+class _LazyPositions(SequenceABC):
+    """The position of every token of a step, worked out when a part first asks (parts that run on
+    the host side of a step do; the kernels read positions on the device)."""
+
+    def __init__(self, seg_q_len: List[int], seg_kv_len: List[int]):
+        self._q, self._kv, self._all = seg_q_len, seg_kv_len, None
+
+    def _list(self) -> List[int]:
+        if self._all is None:
+            self._all = [p for n, kv in zip(self._q, self._kv) for p in range(kv - n, kv)]
+        return self._all
+
+    def __len__(self) -> int:
+        return sum(self._q)
+
+    def __getitem__(self, i):
+        return self._list()[i]
+
+    def __iter__(self):
+        return iter(self._list())
+
+    def __eq__(self, other):
+        return list(self) == list(other)
 
 
 class Engine:
@@ -108,12 +134,60 @@ class Engine:
         With ``greedy`` the largest logit of each wanted place is picked on the device in the same
         launch (the same CUDA graph for steps of single tokens) and the int32 ids come back instead.
         Both live in buffers of the engine: valid until the next step."""
-        cache, vocab = self.cache, self.model.spec.vocab_size
         if not entries:
             return None
         staged = self._stage_single_tokens(entries)
         if staged is not None:
             return self._run(*staged, greedy=greedy)
+        try:
+            slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=len(entries))
+            tok_off = np.zeros(len(entries) + 1, dtype=np.int32)
+            want_off = np.zeros(len(entries) + 1, dtype=np.int32)
+            np.cumsum([len(e.tokens) for e in entries], out=tok_off[1:])
+            np.cumsum([len(e.want) for e in entries], out=want_off[1:])
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
+            wants = np.concatenate([np.asarray(list(e.want), dtype=np.int64).reshape(-1) for e in entries])
+            if tokens.size and (tokens.min() < -2**31 or tokens.max() >= 2**31):
+                raise OverflowError
+            if wants.size and (wants.min() < -2**31 or wants.max() >= 2**31):
+                raise OverflowError
+        except (TypeError, ValueError, OverflowError):
+            self._explain(entries)
+            raise StepError("the step's entries are not lists of whole numbers")
+        return self.step_flat(slots, tok_off, tokens.astype(np.int32), want_off, wants.astype(np.int32), greedy=greedy,
+                              _entries=entries)
+
+    def step_flat(self, slots, tok_off, tokens, want_off, wants, greedy: bool = False, _entries=None) -> Optional[torch.Tensor]:
+        """``step`` for callers that hold the batch as arrays already (the scheduler's plans): entry
+        ``i`` is the request in ``slots[i]`` with tokens ``tokens[tok_off[i]:tok_off[i+1]]`` and wanted
+        places ``wants[want_off[i]:want_off[i+1]]`` (int32 arrays).  Checked and laid out for the
+        device by the cache manager in one native call."""
+        s = len(slots)
+        if s == 0:
+            return None
+        n, n_want = int(tok_off[-1]), int(want_off[-1])
+        stage = self._stage(3 * n + 6 * s + n_want)
+        rc, bad, n, s, n_want, decode_only, total = self.cache.manager.stage_step(
+            slots, tok_off, tokens, want_off, wants, self.model.spec.vocab_size, self.max_step_tokens, stage.numpy())
+        if rc != 0:
+            self._turn ^= 1                          # the staging buffer was not used
+            entries = _entries if _entries is not None else [
+                StepEntry(int(slots[i]), tokens[tok_off[i]:tok_off[i + 1]].tolist(), wants[want_off[i]:want_off[i + 1]].tolist())
+                for i in range(s)]
+            if rc == 2:
+                e = entries[bad]
+                start = self.cache.length(e.slot)
+                raise OutOfPages(f"slot {e.slot}: no pages for positions {start}..{start + len(e.tokens) - 1}")
+            self._explain(entries)
+            raise StepError("the step was refused")
+        seg = stage.numpy()[3 * n:3 * n + 4 * s].reshape(4, s)
+        seg_slot, seg_q_start, seg_q_len, seg_kv_len = (row.tolist() for row in seg)
+        return self._run(None, None, stage, total, n, s, n_want, bool(decode_only), seg_slot, seg_q_start, seg_q_len,
+                         seg_kv_len, _LazyPositions(seg_q_len, seg_kv_len), greedy=greedy)
+
+    def _explain(self, entries: Sequence[StepEntry]) -> None:
+        """Raise the :class:`StepError` that says what is wrong with a step the native staging refused."""
+        cache, vocab = self.cache, self.model.spec.vocab_size
         seen = set()
         n = 0
         for e in entries:
@@ -124,16 +198,11 @@ class Engine:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot}: an entry needs at least one token")
-            if len(e.tokens) == 1:
-                bad = None if 0 <= int(e.tokens[0]) < vocab else e.tokens[0]
-            else:
-                toks = np.asarray(e.tokens)
-                out_of_range = (toks < 0) | (toks >= vocab)
-                bad = toks[out_of_range][0] if out_of_range.any() else None
-            if bad is not None:
-                raise StepError(f"slot {e.slot}: token {bad} is outside the vocabulary of {vocab}")
+            for t in e.tokens:
+                if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < vocab):
+                    raise StepError(f"slot {e.slot}: token {t} is outside the vocabulary of {vocab}")
             for w in e.want:
-                if not (0 <= int(w) < len(e.tokens)):
+                if not (isinstance(w, (int, np.integer)) and 0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")
             if cache.length(e.slot) + len(e.tokens) > cache.max_positions:
                 raise StepError(f"slot {e.slot}: {cache.length(e.slot) + len(e.tokens)} positions exceed the "
@@ -142,51 +211,10 @@ class Engine:
         if n > self.max_step_tokens:
             raise StepError(f"{n} tokens exceed the step limit of {self.max_step_tokens}")
 
-        # pages for every entry, before anything runs
-        cache.flush()
-        starts = []
-        for e in entries:
-            start = cache.length(e.slot)
-            if not cache.reserve(e.slot, start + len(e.tokens)):
-                raise OutOfPages(f"slot {e.slot}: no pages for positions {start}..{start + len(e.tokens) - 1}")
-            starts.append(start)
-
-        s = len(entries)
-        n_want = sum(len(e.want) for e in entries)
-        decode_only = n == s                      # one token per entry
-        total = 3 * n + 4 * s + n_want + (2 * s if decode_only else 0)
-        stage = self._stage(total)
-        buf = stage.numpy()
-        tokens, positions, slots = buf[0:n], buf[n:2 * n], buf[2 * n:3 * n]
-        seg = buf[3 * n:3 * n + 4 * s].reshape(4, s)
-        want = buf[3 * n + 4 * s: 3 * n + 4 * s + n_want]
-        at = w_at = 0
-        seg_slot, seg_q_start, seg_q_len, seg_kv_len = [], [], [], []
-        for i, (e, start) in enumerate(zip(entries, starts)):
-            k = len(e.tokens)
-            tokens[at:at + k] = np.asarray(e.tokens, dtype=np.int32)
-            positions[at:at + k] = np.arange(start, start + k, dtype=np.int32)
-            slots[at:at + k] = e.slot
-            seg[:, i] = (e.slot, at, k, start + k)
-            seg_slot.append(e.slot); seg_q_start.append(at); seg_q_len.append(k); seg_kv_len.append(start + k)
-            for w in e.want:
-                want[w_at] = at + int(w)
-                w_at += 1
-            at += k
-        if decode_only:
-            # one work item per entry for the attention kernels: (segment, first token 0)
-            items = buf[total - 2 * s: total].reshape(s, 2)
-            items[:, 0] = np.arange(s, dtype=np.int32)
-            items[:, 1] = 0
-
-        return self._run(entries, starts, stage, total, n, s, n_want, decode_only, seg_slot, seg_q_start, seg_q_len,
-                         seg_kv_len, positions.tolist(), greedy=greedy)
-
     def _stage_single_tokens(self, entries: Sequence[StepEntry]):
-        """A step of one token per request, checked and laid out by the cache manager in one call
-        (the host's share of such a step is otherwise about 10 us a request, which nothing hides).
-        None when the step is not of that kind or something about it is irregular: the general
-        path then finds the words for it."""
+        """A step of one token per request given as entries: the lists go to the cache manager as
+        they are (no arrays are built).  None when the step is not of that kind or something about
+        it is irregular: the general path then finds the words for it."""
         s = len(entries)
         slots, toks, wanted = [], [], []
         for e in entries:
@@ -266,11 +294,10 @@ class Engine:
                 logits = picks
         else:
             logits = self._graph_step(graph_key, context, want_rows, n_want, greedy)
-        if decode_only and seg_q_len == [1] * s:
+        if decode_only:
             cache.manager.commit_decode(seg_slot)
         else:
-            for e, start in zip(entries, starts):
-                cache.commit(e.slot, start + len(e.tokens))
+            cache.manager.commit_step(stage.numpy()[3 * n:3 * n + 4 * s], s)
         self.steps += 1
         if cache.checks_tables:
             bad = cache.fault()

@@ -227,3 +227,53 @@ def test_needs_by_part_name_make_groups_and_views():
     assert c.parts(1) == ["attn", "memory"] and c.parts(2) == [] and c.parts(6) == ["mixer"]
     assert latent.elements_per_token == 24 and wide_v.elements_per_token == 2 * (16 + 40)
     assert bytes_per_token(needs, torch.bfloat16) == 2 * (4 * 64 + 24 + 2 * 112)
+
+
+def test_staged_step_of_any_shape(host):
+    """stage_step lays out portions of prompts beside single tokens in one call: the layout is what
+    the step function needs (tokens, positions, slots, segments, wanted rows), pages are taken
+    for every entry, and irregular input takes nothing."""
+    m = host.CacheManager([host.GroupConfig(4, 16)], max_slots=4, max_positions=40)
+    a, b, c = (m.open_slot() for _ in range(3))
+    assert m.reserve(a, 5) and m.reserve(c, 2)
+    m.commit(a, 5); m.commit(c, 2)
+    i32 = lambda x: np.asarray(x, dtype=np.int32)
+    out = np.full(128, -7, dtype=np.int32)
+    # a: one decoded token (wanted); b: a portion of 6 (places 0 and 5 wanted); c: a portion of 3 (nothing wanted)
+    slots, tok_off, want_off = i32([a, b, c]), i32([0, 1, 7, 10]), i32([0, 1, 3, 3])
+    tokens, wants = i32([9, 1, 2, 3, 4, 5, 6, 7, 7, 7]), i32([0, 0, 5])
+    rc, bad, T, S, W, decode_only, total = m.stage_step(slots, tok_off, tokens, want_off, wants, 10, 64, out)
+    assert (rc, bad, T, S, W, decode_only) == (0, -1, 10, 3, 3, 0) and total == 3 * 10 + 4 * 3 + 3
+    assert out[0:T].tolist() == tokens.tolist()
+    assert out[T:2 * T].tolist() == [5, 0, 1, 2, 3, 4, 5, 2, 3, 4]
+    assert out[2 * T:3 * T].tolist() == [a] + [b] * 6 + [c] * 3
+    assert out[3 * T:3 * T + 4 * S].reshape(4, S).tolist() == [[a, b, c], [0, 1, 7], [1, 6, 3], [6, 6, 5]]
+    assert out[3 * T + 4 * S:total].tolist() == [0, 1, 6]
+    assert out[total] == -7
+    assert [m.reserved_length(s) for s in (a, b, c)] == [6, 6, 5] and [m.length(s) for s in (a, b, c)] == [5, 0, 2]
+    m.commit_step(out[3 * T:3 * T + 4 * S], S)
+    assert [m.length(s) for s in (a, b, c)] == [6, 6, 5]
+    m.check()
+    # single tokens only: the work items follow the wanted rows
+    rc, bad, T, S, W, decode_only, total = m.stage_step(i32([c, a]), i32([0, 1, 2]), i32([3, 4]), i32([0, 0, 1]), i32([0]), 10, 64, out)
+    assert (rc, T, S, W, decode_only, total) == (0, 2, 2, 1, 1, 6 + 8 + 1 + 4)
+    assert out[6 + 8:6 + 8 + 1].tolist() == [1] and out[6 + 8 + 1:total].tolist() == [0, 0, 1, 0]
+    m.commit_step(out[3 * T:3 * T + 4 * S], S)
+    # irregular input: refused with nothing taken
+    free = m.free_pages(0)
+    bad_steps = [
+        (i32([a, a]), i32([0, 1, 2]), i32([1, 1]), i32([0, 0, 0]), i32([])),      # a slot twice
+        (i32([3]), i32([0, 1]), i32([1]), i32([0, 0]), i32([])),                   # a slot that is not open
+        (i32([a]), i32([0, 1]), i32([10]), i32([0, 0]), i32([])),                  # a token outside the vocabulary
+        (i32([a]), i32([0, 2]), i32([1, 1]), i32([0, 1]), i32([2])),               # a wanted place outside the entry
+        (i32([a]), i32([0, 0]), i32([]), i32([0, 0]), i32([])),                    # an entry without tokens
+        (i32([b]), i32([0, 35]), i32([1] * 35), i32([0, 0]), i32([])),             # past the context of 40
+    ]
+    for args in bad_steps:
+        assert m.stage_step(*args, 10, 64, out)[0] == 1 and m.free_pages(0) == free
+    assert m.stage_step(i32([b]), i32([0, 9]), i32([1] * 9), i32([0, 0]), i32([]), 10, 8, out)[0] == 1   # over the step limit
+    # no pages: says which entry
+    small = host.CacheManager([host.GroupConfig(4, 2)], max_slots=2, max_positions=40)
+    x, y = small.open_slot(), small.open_slot()
+    rc, bad, *_ = small.stage_step(i32([x, y]), i32([0, 4, 9]), i32([1] * 9), i32([0, 0, 0]), i32([]), 10, 64, out)
+    assert (rc, bad) == (2, 1)

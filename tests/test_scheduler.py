@@ -25,8 +25,10 @@ def toy_next(history):
 class ToyRunner:
     """Executes plans against a toy model that checks what the cache must hold."""
 
-    def __init__(self, host, cache, sched):
+    def __init__(self, host, cache, sched, flat=False):
         self.host, self.cache, self.sched = host, cache, sched
+        #: report the picks as an array in the plan's order (the serving loop's way) instead of a dict
+        self.flat = flat
         self.fed = {}       # slot -> tokens the "cache" holds
         self.steps = 0
         self.max_tokens_seen = 0
@@ -48,7 +50,17 @@ class ToyRunner:
                 picked[e.id] = toy_next(held)
         self.max_tokens_seen = max(self.max_tokens_seen, plan.n_tokens)
         assert plan.n_tokens == sum(len(e.tokens) for e in plan.entries)
-        done = self.sched.commit(plan, picked)
+        if self.flat:
+            import numpy as np
+            ids, slots_a, tok_off, tokens, want_off, wants = plan.flat()
+            assert ids.tolist() == [e.id for e in plan.entries] and slots_a.tolist() == [e.slot for e in plan.entries]
+            assert tokens.tolist() == [t for e in plan.entries for t in e.tokens]
+            assert np.diff(tok_off).tolist() == [len(e.tokens) for e in plan.entries]
+            assert np.diff(want_off).tolist() == [int(e.want_logits) for e in plan.entries]
+            assert wants.tolist() == [len(e.tokens) - 1 for e in plan.entries if e.want_logits]
+            done = self.sched.commit_in_order(plan, np.asarray([picked[e.id] for e in plan.entries if e.want_logits], dtype=np.int32))
+        else:
+            done = self.sched.commit(plan, picked)
         self.cache.check()
         self.steps += 1
         return plan, done
@@ -164,7 +176,7 @@ def test_fuzz_many_requests_small_pool(host, seed):
     page = rng.choice([2, 4, 8])
     cache, sched = make(host, n_pages=rng.randint(14, 30), page=page, slots=4, budget=rng.choice([6, 12, 40]),
                         running=rng.randint(2, 4), chunk=rng.choice([0, 3, 8]), positions=128)
-    r = ToyRunner(host, cache, sched)
+    r = ToyRunner(host, cache, sched, flat=seed % 2 == 1)      # every other seed the serving loop's way
     want, outs = {}, {}
     next_id = 0
     for step in range(400):
