@@ -9,7 +9,8 @@
 ids: a prompt is a list of ids (``"1 2 3"`` or ``"1,2,3"``); when the folder holds a
 ``tokenizer.json`` and the ``tokenizers`` package is importable, other text is encoded
 with it and the output decoded.  ``AXON_LOGITS_IDS`` gives ids in place of the prompt
-(``;`` separates sequences) and ``AXON_LOGITS_ALL=N`` prints the top-K of the last N
+(``;`` separates sequences); ``AXON_LOGITS_ALL=N``, ``AXON_LOGITS_PREFIX=N``, ``AXON_LOGITS_EACH=1``
+and ``AXON_LOGITS_NLL=1`` print more positions (see ``_logits_of``): ``ALL`` prints the top-K of the last N
 positions (src/cli.rs:971-1157).  Generated text goes to stdout, speeds to stderr.
 """
 
@@ -139,6 +140,72 @@ def cmd_info(path: str) -> int:
     return 0
 
 
+def _env_count(name: str) -> Optional[int]:
+    v = os.environ.get(name, "").strip()
+    if not v:
+        return None
+    if not v.isdigit():
+        fail(f"{name} needs a whole number, got '{v}'")
+    return int(v)
+
+
+def _logits_of(net, cache, ids: List[int], top_k: int, tok: "_Tok", room: int) -> None:
+    """``axon logits``: the top-k (id, logit, log-probability, text) after the prompt, or, under the
+    oracle hooks of the reference (src/cli.rs:1088-1157), after several of its positions:
+
+    ``AXON_LOGITS_ALL=N``     after each of the last N positions: the rest is fed in batched passes
+                              (no logits), then one decode step each;
+    ``AXON_LOGITS_PREFIX=N``  after each position from N - 1 on: the first N positions in batched
+                              passes (position N - 1 is the last pass's last row), the rest one
+                              decode step each (0 or 1: all decode steps);
+    ``AXON_LOGITS_EACH=1``    with a prefix: every position from N - 1 on is the last row of its own
+                              batched pass over the tokens up to it, on a fresh cache;
+    ``AXON_LOGITS_NLL=1``     also ``nll <position> <next id> <-ln p>`` of the next token of the
+                              sequence, in float64.
+    """
+    import numpy as np
+    all_n = min(_env_count("AXON_LOGITS_ALL") or 0, len(ids))
+    prefix = _env_count("AXON_LOGITS_PREFIX")
+    nll = os.environ.get("AXON_LOGITS_NLL") == "1"
+    each = os.environ.get("AXON_LOGITS_EACH") == "1" and prefix is not None
+
+    def show(row32: "np.ndarray", pos: Optional[int]) -> None:
+        row = row32.astype(np.float64)
+        lse = float(np.log(np.sum(np.exp(row - row.max()))) + row.max())
+        order = np.lexsort((-np.arange(len(row)), -row))[:top_k]
+        if pos is not None:
+            print(f"position {pos}:")
+        for t in order:
+            print(f"{int(t):>8}  {row[t]:>12.6f}  {row[t] - lse:>12.6f}  {tok.decode([int(t)])!r}")
+        if nll and pos is not None and pos + 1 < len(ids):
+            nxt = ids[pos + 1]
+            print(f"nll {pos} {nxt} {lse - row[nxt]:.9f}")
+
+    if not all_n and prefix is None:
+        show(net.prefill_logits(ids, 0, cache), None)
+        cache.close()
+        return
+    print(f"prompt ids ({len(ids)}): {list(ids)}")
+    if prefix is not None:
+        first, batched = min(max(prefix, 1), len(ids)) - 1, prefix > 1
+    else:
+        first, batched = len(ids) - all_n, False
+    last = None
+    if batched:
+        last = net.prefill_logits(ids[:first + 1], 0, cache)
+    elif first > 0:
+        net.feed_batch(ids[:first], 0, cache)
+    for p in range(first, len(ids)):
+        if each and p > first:
+            cache.close()
+            cache = net.new_cache(room)
+            last = net.prefill_logits(ids[:p + 1], 0, cache)
+        elif not batched or p > first:
+            last = net.forward(ids[p], p, cache)[0]
+        show(last, p)
+    cache.close()
+
+
 def run_lm(args: List[str]) -> int:
     from . import api
     from .sampling.sampler import SampleArgs
@@ -215,32 +282,28 @@ def run_lm(args: List[str]) -> int:
     if cmd == "gen":
         n_gen = max(0, min(n_gen, trained - longest))   # the trained context caps generation (src/cli.rs:811-824)
     room = ctx or (longest + n_gen + 1)
+    t_load = time.perf_counter()
     try:
         opts = api.BackendOptions().device(device).max_ctx(room).dtype(dtype).kv(kv).parallel(2)
         net = api.Backend(model, opts)
     except (ValueError, RuntimeError) as e:
         fail(str(e))
+    print(f"load:        {model.n_tensors} tensors, {model.n_bytes / 1e9:.2f} GB in {time.perf_counter() - t_load:.2f} s", file=sys.stderr)
     if verbose:
+        import torch
+        dev = net.engine.rt.device
         print(f"model:       {model.config}", file=sys.stderr)
-        print(f"placed:      {device} {dtype}, ctx {net.ctx}, page size {opts._page_size}", file=sys.stderr)
+        print(f"placed:      {device} {dtype}, ctx {net.ctx}, page size {opts._page_size}, "
+              f"cache pool of {net.engine.cache.n_pages * opts._page_size} positions", file=sys.stderr)
+        print(f"device:      {torch.cuda.memory_allocated(dev) / 1e9:.2f} GB in use after loading, "
+              f"{torch.cuda.max_memory_allocated(dev) / 1e9:.2f} GB at the most", file=sys.stderr)
 
     import numpy as np
     for ids in seqs:
         cache = net.new_cache(room)
         t0 = time.perf_counter()
         if cmd == "logits":
-            all_n = int(os.environ.get("AXON_LOGITS_ALL", "0") or 0)
-            from .engine.step import StepEntry
-            want = list(range(max(0, len(ids) - all_n), len(ids))) if all_n else [len(ids) - 1]
-            rows = net.engine.step([StepEntry(cache.slot, ids, want)]).cpu().numpy().astype(np.float64)
-            for pos, row in zip(want, rows):
-                lse = float(np.log(np.sum(np.exp(row - row.max()))) + row.max())
-                order = np.lexsort((-np.arange(len(row)), -row))[:top_k]
-                if all_n:
-                    print(f"position {pos}:")
-                for t in order:
-                    print(f"{int(t):>8}  {row[t]:>12.6f}  {row[t] - lse:>12.6f}  {tok.decode([int(t)])!r}")
-            cache.close()
+            _logits_of(net, cache, ids, top_k, tok, room)
             continue
         logits = net.prefill_logits_device(ids, 0, cache)
         import torch
@@ -277,6 +340,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             fail("usage: axon info <model>")
         try:
             return cmd_info(args[1])
+        except BrokenPipeError:
+            raise
         except (ValueError, OSError) as e:
             fail(str(e))
     if args[0] in ("gen", "logits"):
@@ -284,10 +349,26 @@ def main(argv: Optional[List[str]] = None) -> int:
     if os.path.isdir(args[0]):
         try:
             return cmd_info(args[0])
+        except BrokenPipeError:
+            raise
         except (ValueError, OSError) as e:
             fail(str(e))
     fail(f"unknown command '{args[0]}' (info, gen, logits)")
 
 
+def run() -> int:
+    """``main`` for the ``axon`` program: a reader that closes the pipe early (``| head``) ends it quietly."""
+    try:
+        rc = main()
+        sys.stdout.flush()
+        return rc
+    except BrokenPipeError:
+        try:
+            sys.stdout.close()
+        except BrokenPipeError:
+            pass
+        return 0
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(run())

@@ -318,9 +318,9 @@ def attention(q, kv, ctx, out, heads: int, scale: float) -> bool:
     if heads % kv.kv_heads or heads // kv.kv_heads > 64 or ctx.segments is None:
         return False
     group = heads // kv.kv_heads
-    # prompt portions at head size 128 take the tcgen05 kernel with 128-row tiles
+    # prompt portions at head size 128 take the tcgen05 kernel with tiles of 256 rows (two sub-tiles of 128)
     use_tc = ENABLED["attention_tc"] and kv.head_dim == 128 and ctx.unit_items is None
-    it = _attention_items(ctx, group, 128 if use_tc else 64)
+    it = _attention_items(ctx, group, 256 if use_tc else 64)
     cu = lib.cuda()
     n_seg = len(ctx.seg_slot)
     if it["n_dec"]:

@@ -15,6 +15,7 @@ everything to float32.
 from __future__ import annotations
 
 import hashlib
+import json
 import os
 from typing import Dict, Iterator, List, Mapping, Optional, Tuple, Union
 
@@ -23,7 +24,7 @@ import torch
 from ..config.base import ModelConfig, architecture_of, write_config_json
 from ..parts.base import part_class
 from ..parts.spec import LayerSpec, ModelSpec, PartSpec, TensorDecl
-from .safetensors_io import Checkpoint, SafetensorsError, write_safetensors
+from .safetensors_io import Checkpoint, SafetensorsError, write_safetensors, write_safetensors_stream
 
 
 class WeightsError(ValueError):
@@ -158,11 +159,39 @@ def random_weights(spec: ModelSpec, seed: int, dtype: torch.dtype, device: Union
 
 
 def write_random_model(folder: str, config: ModelConfig, seed: int, store_dtype: torch.dtype = torch.bfloat16,
-                       std: float = 0.02, gain_std: float = 0.1) -> None:
-    """Write ``config.json`` and ``model.safetensors`` of a seeded random model."""
+                       std: float = 0.02, gain_std: float = 0.1, shards: int = 1) -> None:
+    """Write ``config.json`` and the weights of a seeded random model: ``model.safetensors``, or
+    with ``shards`` > 1 that many files ``model-0000i-of-0000n.safetensors`` of about equal size
+    and the ``model.safetensors.index.json`` that maps every tensor to its file.  Tensors are
+    made and written one at a time, so a model larger than host memory can be written."""
     arch = architecture_of(config.to_dict())
     spec = arch.build_spec(config)
-    tensors = {name: random_tensor(name, decl, seed, std, gain_std).to(store_dtype)
-               for name, decl in expected_tensors(spec).items()}
+    decls = expected_tensors(spec)
+    names = sorted(decls)
+    item = torch.empty((), dtype=store_dtype).element_size()
+    size = {n: item * int(torch.Size(decls[n].shape).numel()) for n in names}
+    produce = lambda n: random_tensor(n, decls[n], seed, std, gain_std).to(store_dtype)
     write_config_json(folder, config)
-    write_safetensors(os.path.join(folder, "model.safetensors"), tensors, {"format": "pt"})
+    if shards <= 1:
+        write_safetensors_stream(os.path.join(folder, "model.safetensors"),
+                                 [(n, store_dtype, tuple(decls[n].shape)) for n in names], produce, {"format": "pt"})
+        return
+    # contiguous runs of the sorted names, cut where the running size passes the next n-th of the whole
+    total, groups, run, acc = sum(size.values()), [], [], 0
+    for n in names:
+        run.append(n)
+        acc += size[n]
+        if len(groups) < shards - 1 and acc >= total * (len(groups) + 1) / shards:
+            groups.append(run)
+            run = []
+    if run:
+        groups.append(run)
+    weight_map = {}
+    for i, group in enumerate(groups):
+        fname = f"model-{i + 1:05d}-of-{len(groups):05d}.safetensors"
+        write_safetensors_stream(os.path.join(folder, fname), [(n, store_dtype, tuple(decls[n].shape)) for n in group],
+                                 produce, {"format": "pt"})
+        weight_map.update({n: fname for n in group})
+    with open(os.path.join(folder, "model.safetensors.index.json"), "w", encoding="utf-8") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=1, sort_keys=True)
+        f.write("\n")

@@ -15,7 +15,7 @@ import mmap
 import os
 import struct
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Mapping, Optional, Tuple
+from typing import Callable, Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -198,29 +198,48 @@ class Checkpoint:
             f.close()
 
 
-def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],
-                      metadata: Optional[Mapping[str, str]] = None) -> None:
-    """Write host tensors to ``path`` in name order, data 8-byte aligned."""
+def write_safetensors_stream(path: str, specs: Sequence[Tuple[str, torch.dtype, Tuple[int, ...]]],
+                             produce: Callable[[str], torch.Tensor],
+                             metadata: Optional[Mapping[str, str]] = None) -> int:
+    """Write a safetensors file whose tensors are made one at a time: ``specs`` lists
+    (name, dtype, shape) in file order, ``produce(name)`` returns each host tensor when its
+    turn comes, so a file larger than memory can be written.  Data is 8-byte aligned.
+    Returns the bytes of tensor data written."""
     header: Dict[str, object] = {}
     if metadata:
         header["__metadata__"] = dict(metadata)
     offset = 0
-    order = sorted(tensors)
-    blobs = []
-    for name in order:
-        t = tensors[name].detach().cpu().contiguous()
-        if t.dtype not in _DTYPE_NAMES:
-            raise SafetensorsError(f"tensor {name}: dtype {t.dtype} cannot be stored")
-        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
-        header[name] = {"dtype": _DTYPE_NAMES[t.dtype], "shape": list(t.shape),
-                        "data_offsets": [offset, offset + len(raw)]}
-        offset += len(raw)
-        blobs.append(raw)
+    for name, dtype, shape in specs:
+        if dtype not in _DTYPE_NAMES:
+            raise SafetensorsError(f"tensor {name}: dtype {dtype} cannot be stored")
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * _DTYPES[_DTYPE_NAMES[dtype]][1]
+        header[name] = {"dtype": _DTYPE_NAMES[dtype], "shape": [int(d) for d in shape],
+                        "data_offsets": [offset, offset + nbytes]}
+        offset += nbytes
     blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
     blob += b" " * ((8 - len(blob) % 8) % 8)
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(blob)))
         f.write(blob)
-        for raw in blobs:
-            f.write(raw)
+        for name, dtype, shape in specs:
+            t = produce(name).detach().cpu().contiguous()
+            if t.dtype != dtype or tuple(t.shape) != tuple(shape):
+                raise SafetensorsError(f"tensor {name}: made as {t.dtype} {tuple(t.shape)}, announced as {dtype} {tuple(shape)}")
+            if t.numel():
+                f.write(t.reshape(-1).view(torch.uint8).numpy().data)
+            del t
+    return offset
+
+
+def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],
+                      metadata: Optional[Mapping[str, str]] = None) -> None:
+    """Write host tensors to ``path`` in name order, data 8-byte aligned.  The tensors are copied
+    before the file is opened, so they may be views of the very file that is being replaced."""
+    order = sorted(tensors)
+    held = {n: tensors[n].detach().cpu().clone() for n in order}
+    write_safetensors_stream(path, [(n, held[n].dtype, tuple(held[n].shape)) for n in order],
+                             lambda n: held.pop(n), metadata)

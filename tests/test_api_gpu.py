@@ -176,6 +176,26 @@ def test_command_line(model_folders):
     assert len(lines) == 3
     assert int(lines[0].split()[0]) == want[0]
     assert abs(float(lines[0].split()[1]) - float(row.max())) < 2e-5 * float(row.abs().max())
+    # the oracle hooks: positions 8.. after a batched prefix of 9, each as a pass of its own, with the next token's -ln p
+    env = dict(os.environ, AXON_LOGITS_IDS=",".join(map(str, ids)), AXON_LOGITS_PREFIX="9", AXON_LOGITS_NLL="1")
+    full = plain.forward(cfg, w, ids)
+    for each in ("0", "1"):
+        p = subprocess.run([axon, "logits", model_folders["B"], "-k", "2", "--dtype", "float32"],
+                           capture_output=True, text=True, timeout=600, env=dict(env, AXON_LOGITS_EACH=each))
+        assert p.returncode == 0, p.stderr[-2000:]
+        out = p.stdout.splitlines()
+        assert out[0] == f"prompt ids (12): {ids}"
+        assert [l for l in out if l.startswith("position")] == [f"position {k}:" for k in range(8, 12)]
+        nll = {int(l.split()[1]): (int(l.split()[2]), float(l.split()[3])) for l in out if l.startswith("nll")}
+        assert sorted(nll) == [8, 9, 10]
+        for pos, (nxt, v) in nll.items():
+            want_nll = float(torch.logsumexp(full[pos], 0) - full[pos][ids[pos + 1]])
+            assert nxt == ids[pos + 1] and abs(v - want_nll) < 1e-3, f"each={each} position {pos}"
+        best = [int(out[k + 1].split()[0]) for k, l in enumerate(out) if l.startswith("position")]
+        assert best == [int(full[k].argmax()) for k in range(8, 12)]
+    p = subprocess.run([axon, "logits", model_folders["B"], "-k", "1", "--dtype", "float32"], capture_output=True, text=True,
+                       timeout=600, env=dict(os.environ, AXON_LOGITS_IDS=",".join(map(str, ids)), AXON_LOGITS_ALL="3"))
+    assert p.returncode == 0 and [l for l in p.stdout.splitlines() if l.startswith("position")] == [f"position {k}:" for k in (9, 10, 11)]
     p = subprocess.run([axon, "gen", model_folders["B"], "1 2", "--temp", "7000"], capture_output=True, text=True, timeout=600)
     assert p.returncode == 2 and "--temp needs a number from 0 to 100" in p.stderr
     p = subprocess.run([axon, "info", model_folders["B"]], capture_output=True, text=True, timeout=600)

@@ -162,3 +162,26 @@ def test_untied_model_without_a_head_is_an_error(tmp_path):
     write_safetensors(str(tmp_path / "model.safetensors"), t)
     with pytest.raises(WeightsError, match="lm_head.weight"):     # src/safetensors.rs:1608-1614
         load_weights(str(tmp_path), qwen2_spec(cfg), torch.bfloat16, "cpu")
+
+
+def test_random_model_in_shards_reads_back_the_same(tmp_path):
+    """A model written as several files with an index holds the bytes of the one-file model, and the
+    loader reads both alike (shards and their index: src/safetensors.rs:347-430)."""
+    import json
+    cfg = config_from_dict(TINY_B)
+    one, many = tmp_path / "one", tmp_path / "many"
+    write_random_model(str(one), cfg, seed=4)
+    write_random_model(str(many), cfg, seed=4, shards=3)
+    files = sorted(p.name for p in many.iterdir())
+    assert files == ["config.json", "model-00001-of-00003.safetensors", "model-00002-of-00003.safetensors",
+                     "model-00003-of-00003.safetensors", "model.safetensors.index.json"]
+    index = json.loads((many / "model.safetensors.index.json").read_text())
+    spec = qwen2_spec(cfg)
+    a = load_weights(str(one), spec, torch.bfloat16, "cpu")
+    b = load_weights(str(many), spec, torch.bfloat16, "cpu")
+    assert set(index["weight_map"]) == set(a) == set(b)
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    sizes = [(many / f).stat().st_size for f in files if f.endswith(".safetensors")]
+    assert max(sizes) < 2 * min(sizes), f"the shards are of very different sizes: {sizes}"
+    assert index["metadata"]["total_size"] == sum(t.numel() * 2 for t in a.values() if t.dtype == torch.bfloat16) + \
+        sum(t.numel() * 2 for t in a.values() if t.dtype == torch.float32)
