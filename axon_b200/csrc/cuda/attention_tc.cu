@@ -34,7 +34,7 @@ constexpr int AT_SOFTMAX_THREADS = AT_SUB * 128, AT_PRODUCERS = 64;
 constexpr int AT_MMA_WARP = AT_SOFTMAX_THREADS / 32;                   // warp 8
 constexpr int AT_PV_WARP = AT_MMA_WARP + 1 + AT_PRODUCERS / 32;        // warp 11
 constexpr int AT_THREADS = AT_SOFTMAX_THREADS + 32 + AT_PRODUCERS + 32; // 8 softmax warps, the Q K^T warp, 2 producer warps, the P V warp
-constexpr int AT_NK = 4, AT_NV = 4;              // stages of the key ring and of the value ring
+constexpr int AT_NK = 3, AT_NV = 3;              // stages of the key ring and of the value ring
 constexpr float AT_LAZY = 8.f;                   // log2 units a row's maximum may grow before O is rescaled
 
 struct AtParams {
@@ -124,11 +124,13 @@ attention_tc_kernel(const AtParams p) {
     constexpr uint32_t KV_BYTES = 2 * AT_BN * 128;              // a tile: two halves [dims 0..63 | 64..127][key][64 dims]
     constexpr uint32_t P_BYTES = AT_BM * 128;                   // [row][64 keys]
     const uint32_t q_sm = base, k_sm = q_sm + AT_SUB * QSUB_BYTES, v_sm = k_sm + AT_NK * KV_BYTES, p_sm = v_sm + AT_NV * KV_BYTES;
-    const uint32_t bars = p_sm + AT_SUB * P_BYTES;
-    // mbarriers, 8 bytes each; s_full and s_free per (sub-tile, score buffer)
+    const uint32_t bars = p_sm + 2 * AT_SUB * P_BYTES;          // two P buffers per sub-tile, used in turn
+    // mbarriers, 8 bytes each; s_full and s_free per (sub-tile, score buffer), p_full and pv_done per
+    // (sub-tile, P buffer): a wait by phase parity may lag its barrier by one phase only, and the
+    // softmax threads can be two tiles ahead of the thread that issues P V
     const uint32_t k_full = bars, k_empty = k_full + 8 * AT_NK, v_full = k_empty + 8 * AT_NK, v_empty = v_full + 8 * AT_NV;
-    const uint32_t s_full = v_empty + 8 * AT_NV, s_free = s_full + 16 * AT_SUB, p_full = s_free + 16 * AT_SUB, pv_done = p_full + 8 * AT_SUB;
-    const uint32_t tmem_slot_addr = pv_done + 8 * AT_SUB;
+    const uint32_t s_full = v_empty + 8 * AT_NV, s_free = s_full + 16 * AT_SUB, p_full = s_free + 16 * AT_SUB, pv_done = p_full + 16 * AT_SUB;
+    const uint32_t tmem_slot_addr = pv_done + 16 * AT_SUB;      // (pv_done: per sub-tile and P buffer)
     volatile uint32_t& tmem_slot = *reinterpret_cast<volatile uint32_t*>(smem_dyn + (tmem_slot_addr - base));
     // tensor memory: two score buffers of 64 columns per sub-tile in columns 0..255, O of the sub-tiles in 256..383 and 384..511
     constexpr uint32_t TMEM_COLS = 512, TMEM_O = 2 * AT_SUB * AT_BN;
@@ -159,8 +161,10 @@ attention_tc_kernel(const AtParams p) {
                 mbar_init(s_full + 16 * g + 8 * b, 1);
                 mbar_init(s_free + 16 * g + 8 * b, 4);      // one arrival per softmax warp of the sub-tile
             }
-            mbar_init(p_full + 8 * g, 4);
-            mbar_init(pv_done + 8 * g, 1);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(p_full + 16 * g + 8 * b, 4);
+                mbar_init(pv_done + 16 * g + 8 * b, 1);
+            }
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -176,7 +180,7 @@ attention_tc_kernel(const AtParams p) {
 
     if (warp > AT_MMA_WARP && warp < AT_PV_WARP) {
         // ================= producers.  Step j asks for K(j) and V(j - 1) (one commit group); two
-        // steps stay in flight: when step j's copies are asked for, step j - 2's are waited for
+        // a step stays in flight: when step j's copies are asked for, step j - 1's are waited for
         // and announced.
         const int tid = threadIdx.x - (AT_SOFTMAX_THREADS + 32);
         AtGather g;
@@ -217,15 +221,13 @@ attention_tc_kernel(const AtParams p) {
                 else at_gather_rows<CHECKED>(g, p.kv, tile, key_base + t * AT_BN, v_plane);
             }
             asm volatile("cp.async.commit_group;");
-            if (j >= 2) {
-                at_cp_async_wait<2>();
-                announce(j - 2);
+            if (j >= 1) {
+                at_cp_async_wait<1>();           // one step stays in flight
+                announce(j - 1);
             }
 #pragma unroll
             for (int q = 0; q < 4; ++q) { pg_v[q] = pg_k[q]; pg_k[q] = pg_next[q]; }
         }
-        at_cp_async_wait<1>();
-        announce(n_tiles - 1);
         at_cp_async_wait<0>();
         announce(n_tiles);
     } else if (warp <= AT_MMA_WARP) {
@@ -291,9 +293,9 @@ attention_tc_kernel(const AtParams p) {
                 mbar_wait_idle(v_full + 8 * vs, (i / AT_NV) & 1, 4);
                 const uint32_t vt = v_sm + vs * KV_BYTES;
                 for (int g = 0; g < n_sub; ++g) {
-                    mbar_wait_idle(p_full + 8 * g, i & 1, 4);
+                    mbar_wait_idle(p_full + 16 * g + 8 * (i & 1), (i >> 1) & 1, 4);
                     tc_fence_after();
-                    const uint32_t pg = p_sm + (uint32_t)g * P_BYTES;
+                    const uint32_t pg = p_sm + (uint32_t)(2 * g + (i & 1)) * P_BYTES;
 #pragma unroll
                     for (int k = 0; k < AT_BN / TC_UMMA_K; ++k) {
                         const uint64_t da = smem_desc(pg) + (uint64_t)(2 * k);
@@ -301,7 +303,7 @@ attention_tc_kernel(const AtParams p) {
                         const uint64_t db = smem_desc_mn(vt + (uint32_t)k * 2048u, AT_BN * 128);
                         umma(tmem + TMEM_O + (uint32_t)(g * AT_HD), da, db, idesc_o, (i | k) ? 1u : 0u);
                     }
-                    umma_commit(pv_done + 8 * g);
+                    umma_commit(pv_done + 16 * g + 8 * (i & 1));
                 }
                 umma_commit(v_empty + 8 * vs);
             }
@@ -313,7 +315,7 @@ attention_tc_kernel(const AtParams p) {
         const int R = g * AT_BM + row;                          // row of the whole tile
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tmem_o = tmem + TMEM_O + (uint32_t)(g * AT_HD) + lane_addr;
-        const uint32_t p_row = p_sm + (uint32_t)g * P_BYTES + (uint32_t)row * 128u;
+        const uint32_t p_rows = p_sm + (uint32_t)(2 * g) * P_BYTES + (uint32_t)row * 128u;      // this row in the sub-tile's first P buffer
         const int my_pos = R < rows_used ? pos0 + R / p.group : -1;          // unused rows see no key
         const int my_lo = p.window > 0 ? my_pos - p.window + 1 : 0;
         // positions of the sub-tile's first and last used row: a tile all of them see whole needs no mask
@@ -358,7 +360,7 @@ attention_tc_kernel(const AtParams p) {
             } else if (__any_sync(0xffffffffu, m_new > m_use + AT_LAZY)) {
                 // the whole warp brings its rows of O to their new maxima (tensor memory access is per
                 // warp); the product that last added to O must be through
-                mbar_wait(pv_done + 8 * g, (it - 1) & 1, 2);
+                mbar_wait(pv_done + 16 * g + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1, 2);
                 __syncwarp();
                 tc_fence_after();
                 const float corr = ex2(m_use - (m_new == -INFINITY ? 0.f : m_new));
@@ -375,8 +377,9 @@ attention_tc_kernel(const AtParams p) {
                 tmem_st_wait();
             }
             const float neg = m_use == -INFINITY ? 0.f : -m_use;
-            // P's buffer is free once the product of the tile before has read it
-            if (it > 0) mbar_wait(pv_done + 8 * g, (it - 1) & 1, 2);
+            // P goes to the buffer that the product of the tile before the last has read
+            if (it > 1) mbar_wait(pv_done + 16 * g + 8 * (it & 1), ((it - 2) >> 1) & 1, 2);
+            const uint32_t p_row = p_rows + (uint32_t)(it & 1) * P_BYTES;
             // ---- P = exp2(s - m) as bfloat16 into shared memory, and the row's sum
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
@@ -401,10 +404,10 @@ attention_tc_kernel(const AtParams p) {
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(s_free + 16 * g + 8 * (it & 1));       // the score buffer may take the tile after the next
-                mbar_arrive(p_full + 8 * g);
+                mbar_arrive(p_full + 16 * g + 8 * (it & 1));
             }
         }
-        mbar_wait(pv_done + 8 * g, (n_tiles - 1) & 1, 2);        // the last P V is done
+        mbar_wait(pv_done + 16 * g + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, 2);        // the last P V is done
         __syncwarp();
         tc_fence_after();
         {
@@ -462,8 +465,8 @@ AXON_API int axon_attention_tc(const void* q, const void* pool, void* out, const
     p.kv = to_paged(layout);
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    constexpr size_t smem = AT_SUB * 2 * AT_BM * 128 + (AT_NK + AT_NV) * (2 * AT_BN * 128) + AT_SUB * AT_BM * 128 +
-                            8 * (2 * AT_NK + 2 * AT_NV + 6 * AT_SUB) + 16;
+    constexpr size_t smem = AT_SUB * 2 * AT_BM * 128 + (AT_NK + AT_NV) * (2 * AT_BN * 128) + 2 * AT_SUB * AT_BM * 128 +
+                            8 * (2 * AT_NK + 2 * AT_NV + 8 * AT_SUB) + 16;
     static_assert(smem <= 227 * 1024, "the tiles do not fit shared memory");
     if (p.kv.fault != nullptr) {
         if (int st = ensure_dynamic_smem<attention_tc_kernel<true>>(smem, "axon_attention_tc")) return st;
