@@ -637,24 +637,35 @@ static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, cons
 }
 
 // The tile shape for a product: among (rows 128 or 256) x (columns 128, 192, 224, 256) the one
-// with the least modelled time.  The model: operand bytes all CTAs pull from L2
-// ((rows + columns) * K * 2 per tile) against what L2 delivers, and whole waves of tiles on 148
-// SMs against the rate one SM sustains on a 256 x 256 tile (12.7 TFLOP/s measured at K = 18944).
-// It picks 256 x 224 where that fills 128 SMs instead of 112 (3584 columns: measured 186 us
-// against 197 us at K = 18944) and 256 x 256 for 4608 and 37888 columns.
+// with the least modelled time.  What bounds this kernel is the feed of operands from L2: an SM
+// pulls at most about 99 GB/s, and all SMs together about 12.9 TB/s (87 GB/s each when every SM
+// has a tile); a tile needs (rows + columns) * K * 2 bytes.  So a wave of tiles takes the bytes
+// of one tile over the rate an SM gets with that many SMs busy (or the tile's math at 15.2
+// TFLOP/s an SM, which never binds for these shapes), and a launch takes its full waves, its
+// last partial wave, and 3 us a wave.  Measured against every shape at the 7B, 1.5B and 32B
+// widths with 2,048 and 8,192 rows: the model is within 5 % of the times, and its choice within
+// 7 % of the best shape (before, with a model fitted at the 7B widths only, up to 15 % off at
+// K = 8,960 and K = 27,648).  It picks 256 x 224 where that fills 128 SMs instead of 112 (3584
+// columns: 186 us against 197 us at K = 18944) and 256 x 256 for 4608 and 37888 columns.
 struct TileShape { int rm, bn; };
+static double modelled_time(int M, int N, int K, int rows, int bn) {
+    const long long tiles = (long long)((M + rows - 1) / rows) * ((N + bn - 1) / bn);
+    const double bytes = (double)(rows + bn) * K * 2, math = (double)rows * bn * K * 2 / 15.2e12;
+    const long long full = tiles / 148, rest = tiles % 148;
+    auto wave = [&](long long busy) {
+        const double rate = 12.9e12 / (double)busy < 99e9 ? 12.9e12 / (double)busy : 99e9;
+        const double feed = bytes / rate;
+        return (feed > math ? feed : math) + 3e-6;
+    };
+    return (double)full * wave(148) + (rest ? wave(rest) : 0.0);
+}
 static TileShape choose_tile(int M, int N, int K) {
     const int bns[4] = {256, 224, 192, 128};
     TileShape best{1, 256};
     double best_t = 1e30;
     for (int rm = (M > TC_BM ? 2 : 1); rm >= 1; --rm) {
         for (int bn : bns) {
-            const int rows = rm * TC_BM;
-            const long long tiles = (long long)((M + rows - 1) / rows) * ((N + bn - 1) / bn);
-            const double feed = (double)tiles * (rows + bn) * K * 2 / 12.9e12;
-            const double waves = (double)((tiles + 147) / 148);
-            const double compute = waves * (double)rows * bn * K * 2 / 12.7e12;
-            const double t = (feed > compute ? feed : compute) + 3e-6 * waves;
+            const double t = modelled_time(M, N, K, rm * TC_BM, bn);
             if (t < best_t * 0.98) { best_t = t; best = TileShape{rm, bn}; }
         }
     }
