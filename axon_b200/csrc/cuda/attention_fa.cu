@@ -142,6 +142,7 @@ template <int HD, bool CHECKED> struct KvLoader {
     int n_pages;
     int ps, pages_per_tile, last_page, kv_len, r0;
     int in_page[ITER], page_of[ITER];
+    int ahead[ITER], ahead_tile;    // table entries of tile `ahead_tile`, asked for while the tile before was loaded
     uint32_t dst[ITER];
 
     __device__ __forceinline__ void init(const __nv_bfloat16* pool, const PagedKv& kv, int slot, int kvh, int kv_len_) {
@@ -153,6 +154,7 @@ template <int HD, bool CHECKED> struct KvLoader {
         page_stride = kv.page_stride; v_off = kv.v_offset;
         pages_per_tile = FA_BN % ps == 0 ? FA_BN / ps : 0;
         last_page = (kv_len - 1) / ps;
+        ahead_tile = -1;
 #pragma unroll
         for (int j = 0; j < ITER; ++j) {
             const int r = r0 + RPP * j;
@@ -165,15 +167,26 @@ template <int HD, bool CHECKED> struct KvLoader {
         if ((unsigned)entry > (unsigned)n_pages) { fault[1] = (unsigned)entry; fault[0] = 1u; return n_pages; }
         return entry;
     }
+    __device__ __forceinline__ void fetch_entries(int tile) {
+        const int first = tile * pages_per_tile;
+#pragma unroll
+        for (int j = 0; j < ITER; ++j) ahead[j] = bt[min(first + page_of[j], last_page)];
+        ahead_tile = tile;
+    }
     // rows past the request's length read its last page (fast path) or last position: finite data, masked later
-    __device__ __forceinline__ void load(uint32_t k_tile, uint32_t v_tile, int key0) const {
+    __device__ __forceinline__ void load(uint32_t k_tile, uint32_t v_tile, int key0) {
         if (pages_per_tile) {
-            const int first = (key0 / FA_BN) * pages_per_tile;
+            // Tiles are asked for in ascending order, so the entries of the next one are requested
+            // here and are in registers when its turn comes: otherwise every tile's copies wait
+            // for a read of the table first.  The tables are complete before the step starts.
+            const int tile = key0 / FA_BN;
+            if (ahead_tile != tile) fetch_entries(tile);
             // every table entry is loaded before any is checked: a check may store (the fault
             // record), and loads behind a possible store are not issued together
             int page[ITER];
 #pragma unroll
-            for (int j = 0; j < ITER; ++j) page[j] = bt[min(first + page_of[j], last_page)];
+            for (int j = 0; j < ITER; ++j) page[j] = ahead[j];
+            fetch_entries(tile + 1);
             if (CHECKED) {
 #pragma unroll
                 for (int j = 0; j < ITER; ++j) page[j] = checked(page[j]);
@@ -365,8 +378,11 @@ attention_fa_kernel(const FaParams p) {
                 loader.load(k_sm + abuf * TILE_BYTES, v_sm + abuf * TILE_BYTES, ahead * FA_BN);
             cp_async_commit();
         }
-        if (DECODE && tile == t_begin) cp_async_wait_all();   // queries included
-        else cp_async_wait_pending<NST - 1>();                // this tile's group (and every older one) has landed
+        // this tile's group (and every older one) has landed.  Decode: the prologue made NST
+        // groups (the last holds the queries and the early tiles with new positions), so at the
+        // first tile only the group just committed may still be on its way
+        if (DECODE && tile == t_begin) cp_async_wait_pending<1>();
+        else cp_async_wait_pending<NST - 1>();
         __syncthreads();
         if (DECODE && tile == t_begin) {
 #pragma unroll
@@ -472,40 +488,54 @@ attention_fa_kernel(const FaParams p) {
     // ---- decode: merge the 4 warps (each saw a quarter of every tile's keys)
     cp_async_wait_all();
     __syncthreads();
-    float* mo = reinterpret_cast<float*>(smem_raw + BM * HD * 2);   // [4][16][HD] over the K/V tiles
-    float* mml = mo + 4 * 16 * HD;                                   // [4][16][2]
+    constexpr int MS = HD + 8;     // row stride in floats: the 8 rows of a warp's store fall on different banks
+    float* mo = reinterpret_cast<float*>(smem_raw + BM * HD * 2);   // [4][16][MS] over the K/V tiles
+    float* mml = mo + 4 * 16 * MS;                                   // [4][16][2]
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
-        float* a = mo + ((warp * 16 + g) * HD) + j * 8 + 2 * t;
-        float* b = mo + ((warp * 16 + g + 8) * HD) + j * 8 + 2 * t;
-        a[0] = o[j][0]; a[1] = o[j][1]; b[0] = o[j][2]; b[1] = o[j][3];
+        if (g < rows_used)
+            *reinterpret_cast<float2*>(mo + (warp * 16 + g) * MS + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+        if (g + 8 < rows_used)
+            *reinterpret_cast<float2*>(mo + (warp * 16 + g + 8) * MS + j * 8 + 2 * t) = make_float2(o[j][2], o[j][3]);
     }
     if (t == 0) {
         mml[(warp * 16 + g) * 2] = m_a; mml[(warp * 16 + g) * 2 + 1] = l_a;
         mml[(warp * 16 + g + 8) * 2] = m_b; mml[(warp * 16 + g + 8) * 2 + 1] = l_b;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < 16 * HD; e += FA_THREADS) {
-        const int r = e / HD, d = e % HD;
-        if (r >= rows_used) continue;
-        float m = -INFINITY;
+    {
+        // a thread owns one row and every 8th group of 4 columns: the warps' weights once per thread
+        const int r = threadIdx.x >> 3, c4 = (threadIdx.x & 7) * 4;
+        if (r < rows_used) {
+            float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
-        const float use = (m == -INFINITY) ? 0.f : m;
-        float l = 0.f, acc = 0.f;
+            for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
+            const float use = (m == -INFINITY) ? 0.f : m;
+            float f[4], l = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(mml[(w * 16 + r) * 2] - use);
-            l += mml[(w * 16 + r) * 2 + 1] * f;
-            acc += mo[(w * 16 + r) * HD + d] * f;
-        }
-        if (p.n_splits == 1) {
+            for (int w = 0; w < 4; ++w) {
+                f[w] = exp2f(mml[(w * 16 + r) * 2] - use);
+                l += mml[(w * 16 + r) * 2 + 1] * f[w];
+            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
             const int tok = q_start + tok0 + r / p.group, head = kvh * p.group + r % p.group;
-            p.out[((long long)tok * p.heads + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-        } else {
             const long long base = (((long long)item * gridDim.y + kvh) * p.n_splits + split) * 16 + r;
-            p.part_o[base * HD + d] = acc;
-            if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
+#pragma unroll
+            for (int d = c4; d < HD; d += 32) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * MS + d);
+                    acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
+                }
+                if (p.n_splits == 1) {
+                    *reinterpret_cast<uint2*>(p.out + ((long long)tok * p.heads + head) * HD + d) =
+                        make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+                } else {
+                    *reinterpret_cast<float4*>(p.part_o + base * HD + d) = acc;
+                }
+            }
+            if (p.n_splits > 1 && c4 == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
         }
     }
     if (p.n_splits == 1 || p.counters == nullptr) return;
@@ -658,7 +688,7 @@ template <int HD, bool DECODE, bool CHECKED>
 static int launch_fa(const FaParams& p, int n_items, int kv_heads, cudaStream_t stream) {
     constexpr int BM = DECODE ? 16 : 64;
     constexpr size_t tiles = (DECODE ? (size_t)BM * HD * 2 : 0) + 2 * (DECODE ? 3 : 2) * (size_t)FA_BN * HD * 2;
-    constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float) : 0;
+    constexpr size_t merge = DECODE ? (size_t)BM * HD * 2 + (4 * 16 * (HD + 8) + 4 * 16 * 2) * sizeof(float) : 0;
     constexpr size_t smem = tiles > merge ? tiles : merge;
     if (int st = ensure_dynamic_smem<attention_fa_kernel<HD, DECODE, CHECKED>>(smem, "axon_attention_fa")) return st;
     dim3 grid(n_items, kv_heads, DECODE ? p.n_splits : 1);

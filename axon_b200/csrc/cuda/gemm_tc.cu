@@ -79,6 +79,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m_tile = blockIdx.x % m_tiles, n_tile = blockIdx.x / m_tiles;
     const int m0 = m_tile * TC_BM * RM, n0 = n_tile * BN;
     const int k_stages = (K + TC_BK - 1) / TC_BK;
+    // the kernel after this one may begin its own set-up; this one fills its ring with weights
+    // and waits for the kernels before it only where it first needs the activations
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -101,9 +104,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-            for (int ks = 0; ks < k_stages; ++ks) {
+            const int early = k_stages < STAGES ? k_stages : STAGES;
+            for (int ks = 0; ks < early; ++ks) {           // weights: nothing in a step writes them
+                mbar_expect_tx(full0 + 8 * ks, STAGE_BYTES);
+                tma_load_2d(smem_base + ks * STAGE_BYTES + A_BYTES, &map_w, ks * TC_BK, n0, full0 + 8 * ks);
+            }
+            pdl_wait();
+            for (int ks = 0; ks < early; ++ks)
+                tma_load_2d(smem_base + ks * STAGE_BYTES, &map_a, ks * TC_BK, m0, full0 + 8 * ks);
+            for (int ks = early; ks < k_stages; ++ks) {
                 const int s = ks % STAGES;
-                if (ks >= STAGES) mbar_wait(empty0 + 8 * s, ((ks / STAGES) - 1) & 1, 0);
+                mbar_wait(empty0 + 8 * s, ((ks / STAGES) - 1) & 1, 0);
                 const uint32_t sa = smem_base + s * STAGE_BYTES, sw = sa + A_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(sa, &map_a, ks * TC_BK, m0, full0 + 8 * s);
@@ -146,6 +157,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_wait(tmem_full, 0, 2, stuck_wait_limit ? stuck_wait_limit : TC_WAIT_LIMIT);
         __syncwarp();
         tc_fence_after();
+        pdl_wait();          // before the output is read or written (the producer passed this long ago)
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
         if constexpr (TMA_OUT) {
@@ -623,7 +635,7 @@ static int launch_tc(int epi, const CUtensorMap& ma, const CUtensorMap& mw, cons
 #define AXON_TC_LAUNCH(E)                                                                                          \
     {                                                                                                              \
         if (int st = ensure_dynamic_smem<gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT>>(smem, "axon_gemm_tc")) return st; \
-        gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT><<<grid, block, smem, stream>>>(ma, mw, mo, bias, out, M, N, K, ldo, m_tiles, stuck_wait_limit); \
+        launch_pdl(gemm_tc_kernel<BN, STAGES, E, RM, TMA_OUT>, grid, block, smem, stream, ma, mw, mo, bias, out, M, N, K, ldo, m_tiles, stuck_wait_limit); \
     }
     switch (epi) {
         case TC_STORE_F32: AXON_TC_LAUNCH(TC_STORE_F32) break;
@@ -672,9 +684,76 @@ static TileShape choose_tile(int M, int N, int K) {
     return best;
 }
 
+
+// How the swapped kernel would cut a product: token columns per CTA, blocks of tokens, K slabs.
+struct SwapPlan { int ntok, blocks, tiles, splits; bool wide; };
+static SwapPlan plan_swapped(int M, int N, int K, int target_ctas, long long partial_floats, int n_counters) {
+    SwapPlan p;
+    // tokens are the MMA's columns: padded to 16 .. 256, and in blocks of 256 beyond that
+    p.ntok = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    p.blocks = (M + p.ntok - 1) / p.ntok;
+    const int m_pad = p.blocks * p.ntok, tiles128 = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
+    // many rows: 256-row tiles halve the CTA count (no split then)
+    // (measured at 7B sizes: with 2 x target tiles, two 128-row CTAs per SM and six stages beat
+    // one 256-row CTA with three; the wide tile pays off only from several waves on)
+    p.wide = p.ntok <= 32 && target_ctas > 0 && tiles128 >= 4 * target_ctas;
+    p.tiles = p.wide ? (N + 255) / 256 : tiles128;
+    // few rows: as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
+    p.splits = 1;
+    if (!p.wide && partial_floats > 0 && p.tiles * p.blocks <= n_counters && p.tiles * p.blocks < target_ctas) {
+        p.splits = (target_ctas + p.tiles * p.blocks / 2) / (p.tiles * p.blocks);
+        if (p.splits > k_total / 4) p.splits = k_total / 4;
+        const long long fit = partial_floats / ((long long)p.tiles * m_pad * 128);
+        if (p.splits > fit) p.splits = (int)fit;
+        if (p.splits < 1) p.splits = 1;
+    }
+    const int per_split = (k_total + p.splits - 1) / p.splits;
+    p.splits = (k_total + per_split - 1) / per_split;
+    return p;
+}
+
+// Modelled time of the swapped kernel inside a chain of kernels: a fixed 5.5 us, the weights at
+// the rate of memory (a block of 256 tokens beyond the first re-reads them from L2 at about a
+// third of that cost), and per token row what the epilogue moves: N * splits * 8 bytes at about
+// 1 TB/s (partial sums written and read back; unsplit, the scattered stores of the transposed
+// tile cost about as much).  A split product that leaves its partial sums to the reader of its
+// output (`deferred`) only writes them, all CTAs at once: N * splits * 4 bytes at about 3.3 TB/s
+// (the reader's share is in the fixed part).  Many rows are bound by the MMAs instead, at about
+// 0.7 PFLOP/s (0.9 deferred).  Fitted to captured chains of each product of the 1.5B, 7B and 32B widths at
+// 32 .. 1,024 rows, and to decode steps of 64 .. 256 requests for the deferred products.
+static double modelled_time_swapped(int M, int N, int K, int target_ctas, bool deferred) {
+    const SwapPlan p = plan_swapped(M, N, K, target_ctas, 1LL << 40, 1 << 30);
+    const double weights = (double)N * K * 2 / 6.5e12 * (1.0 + 0.3 * (p.blocks - 1));
+    const double rows = (double)M * N * p.splits * ((deferred && p.splits > 1) ? 1.2e-12 : 8e-12);
+    // (the transposed epilogue that folds or applies SwiGLU itself costs the MMAs' rate a fifth more)
+    const double math = 2.0 * M * N * K / ((deferred && p.splits > 1) ? 0.9e15 : 0.7e15);
+    const double mem = weights + rows;
+    return 5.5e-6 + (mem > math ? mem : math);
+}
+static double modelled_time_tiled(int M, int N, int K) {
+    const TileShape ts = choose_tile(M, N, K);
+    // never faster than reading the operands once from memory (few rows of a wide product)
+    const double tiles = modelled_time(M, N, K, ts.rm * TC_BM, ts.bn), once = ((double)N + M) * K * 2 / 6.5e12 + 3e-6;
+    return tiles > once ? tiles : once;
+}
+
 }  // namespace axon
 
 using namespace axon;
+
+// Which of the two kernels a product should take: nonzero for the swapped one (axon_gemm_tc_small).
+// Up to 32 rows always (decode steps: the token columns are narrow and nothing else comes close);
+// beyond 1,024 never (it does not take them); between, whichever the two models call faster.
+// `deferred`: the caller lets a split product leave its partial sums to the reader of the output.
+AXON_API int axon_gemm_prefers_swapped(int M, int N, int K, int target_ctas, int deferred) {
+    if (M <= 32) return 1;
+    if (M > 1024) return 0;
+    return modelled_time_swapped(M, N, K, target_ctas, deferred != 0) < modelled_time_tiled(M, N, K) ? 1 : 0;
+}
+// The models' times in microseconds (kind 0: swapped, 1: tiled, 2: swapped and deferred), for tests and reports.
+AXON_API double axon_gemm_modelled_us(int kind, int M, int N, int K, int target_ctas) {
+    return 1e6 * (kind == 1 ? modelled_time_tiled(M, N, K) : modelled_time_swapped(M, N, K, target_ctas, kind == 2));
+}
 
 // For tests and measurements: force the tile shape (rows 1 or 2 times 128; columns 128, 192,
 // 224 or 256); rm 0 gives the choice back to the model.
@@ -773,26 +852,10 @@ AXON_API int axon_gemm_tc_small(const void* a, const void* w, const float* bias,
     if (K <= 0 || K % 8) { set_error("axon_gemm_tc_small: K %d must be a positive multiple of 8", K); return AXON_BAD_ARGUMENT; }
     if (((uintptr_t)a | (uintptr_t)w) & 15) { set_error("axon_gemm_tc_small: operands must be 16-byte aligned"); return AXON_BAD_ARGUMENT; }
     if (epilogue == TC_SWIGLU && (N % 2)) { set_error("axon_gemm_tc_small: SwiGLU needs an even number of columns"); return AXON_BAD_ARGUMENT; }
-    // tokens are the MMA's columns: padded to 16 .. 256, and in blocks of 256 beyond that
-    const int ntok = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    const int blocks = (M + ntok - 1) / ntok, m_pad = blocks * ntok;
-    const int tiles128 = (N + 127) / 128, k_total = (K + TC_BK - 1) / TC_BK;
-    // many rows: 256-row tiles halve the CTA count (no split then)
-    // (measured at 7B sizes: with 2 x target tiles, two 128-row CTAs per SM and six stages beat
-    // one 256-row CTA with three; the wide tile pays off only from several waves on)
-    const bool wide = ntok <= 32 && target_ctas > 0 && tiles128 >= 4 * target_ctas;
-    const int tiles = wide ? (N + 255) / 256 : tiles128;
-    // few rows: as many K slabs as it takes to have about `target_ctas` CTAs, each at least 4 stages long
-    int splits = 1;
-    if (!wide && partial != nullptr && counters != nullptr && tiles * blocks <= n_counters && tiles * blocks < target_ctas) {
-        splits = (target_ctas + tiles * blocks / 2) / (tiles * blocks);
-        if (splits > k_total / 4) splits = k_total / 4;
-        const long long fit = partial_floats / ((long long)tiles * m_pad * 128);
-        if (splits > fit) splits = (int)fit;
-        if (splits < 1) splits = 1;
-    }
-    const int per_split = (k_total + splits - 1) / splits;
-    splits = (k_total + per_split - 1) / per_split;
+    const SwapPlan sp = plan_swapped(M, N, K, target_ctas, (partial != nullptr && counters != nullptr) ? partial_floats : 0, n_counters);
+    const int ntok = sp.ntok, m_pad = sp.blocks * sp.ntok, tiles = sp.tiles, splits = sp.splits;
+    const bool wide = sp.wide;
+    const int k_total = (K + TC_BK - 1) / TC_BK, per_split = (k_total + splits - 1) / splits;
     const bool deferred = defer && splits > 1 && (epilogue == TC_STORE_F32 || epilogue == TC_RESIDUAL);
     if (plan) { plan[0] = splits; plan[1] = m_pad; plan[2] = deferred ? 1 : 0; }
     if (deferred) counters = nullptr;                 // the kernel stops after writing its partial tile

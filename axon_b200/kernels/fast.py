@@ -16,18 +16,24 @@ from . import lib
 from .lib import check
 
 EPI_STORE_F32, EPI_STORE_BF16, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-#: Up to SMALL_M rows a product always takes the kernel that has the tokens as the MMA's columns
-#: and streams each weight row once; up to SWAP_MAX_ROWS it still does when the 256 x 256 tiles
-#: of the other kernel would leave most SMs without one (measured at 7B sizes, 128 rows: down
-#: projection 57 us against 102 us; gate/up, 148 tiles, 96 us against 63 us).
-SMALL_M = 64
+#: Which of the two tcgen05 kernels a product takes.  The swapped one has the tokens as the MMA's
+#: columns and streams each weight row once: always up to 32 rows, never beyond 1,024, and between
+#: those whichever the launchers' two time models call faster (``axon_gemm_prefers_swapped``:
+#: products that may leave their partial sums to the reader, q/k/v, o and down in the standard
+#: block, stay swapped up to a few hundred rows; wide products that may not, gate/up and the head,
+#: leave it from 33 or 64 rows on).  SWAP_RULE: "model", or for tests and measurements
+#: "always" (wherever the swapped kernel takes the size) and "never".
+SWAP_RULE = "model"
 SWAP_MAX_ROWS = 1024
 
 
-def _takes_swapped_kernel(M: int, N: int) -> bool:
-    if M <= SMALL_M:
-        return True
-    return M <= SWAP_MAX_ROWS and -(-M // 256) * -(-N // 256) < 100
+def _takes_swapped_kernel(M: int, N: int, K: int, deferred: bool = False) -> bool:
+    """``deferred``: the caller takes a PendingFold (a split product may skip its own fold)."""
+    if SWAP_RULE == "never":
+        return False
+    if SWAP_RULE == "always":
+        return M <= SWAP_MAX_ROWS
+    return bool(lib.cuda().axon_gemm_prefers_swapped(M, N, K, SPLIT_TARGET_CTAS, int(deferred and DEFER_FOLD)))
 
 #: switches for tests that compare a tuned kernel with the plain one
 ENABLED = {"gemm_tc_small": True, "gemm_tc": True, "attention_prefill": True,
@@ -136,8 +142,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         epi = EPI_STORE_BF16
     else:
         return False
-    if _takes_swapped_kernel(M, N):
-        ran = _gemm_small(a, w, bias, out, epi, M, N, K, defer and out.is_contiguous())
+    defer = defer and out.is_contiguous() and epi in (EPI_STORE_F32, EPI_RESIDUAL)
+    if _takes_swapped_kernel(M, N, K, defer):
+        ran = _gemm_small(a, w, bias, out, epi, M, N, K, defer)
         if ran:
             return ran
     if ENABLED["gemm_tc"]:
@@ -162,7 +169,7 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
         return False
     M, K = h.shape
     N = w_gate_up.shape[0]
-    if _takes_swapped_kernel(M, N) and _gemm_small(h, w_gate_up, None, act, EPI_SWIGLU, M, N, K):
+    if _takes_swapped_kernel(M, N, K) and _gemm_small(h, w_gate_up, None, act, EPI_SWIGLU, M, N, K):
         return True
     if ENABLED["gemm_tc"]:
         check(lib.cuda().axon_gemm_tc(h.data_ptr(), w_gate_up.data_ptr(), None, act.data_ptr(), EPI_SWIGLU,

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "axon_gemm_tc_clear_status": [],
     "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, c_int,
                            ctypes.POINTER(c_int), P],
+    "axon_gemm_prefers_swapped": [c_int, c_int, c_int, c_int, c_int],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
     "axon_attention_fa_decode_fused": [P, P, c_int, c_int, P, P, c_int, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int,
@@ -110,6 +111,8 @@ def cuda() -> ctypes.CDLL:
         lib.axon_topk_max.restype = c_int
         lib.axon_topk_max.argtypes = []
         lib.axon_gemm_tc_force_tile.restype = None
+        lib.axon_gemm_modelled_us.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.axon_gemm_modelled_us.restype = ctypes.c_double
         lib.axon_gemm_tc_force_tile.argtypes = [c_int, c_int]
         lib.axon_gemm_tc_force_plain_out.restype = None
         lib.axon_gemm_tc_force_plain_out.argtypes = [c_int]

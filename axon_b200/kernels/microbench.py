@@ -108,9 +108,9 @@ def main() -> int:
             out = torch.zeros(a.m, a.n, dtype=torch.bfloat16 if a.epilogue == "bf16" else torch.float32, device=DEV)
             fn = lambda: fast.gemm(x, w, out, None, a.epilogue == "residual")
         if a.kernel == "gemm_small_m":
-            fast.SMALL_M = fast.SWAP_MAX_ROWS = 1024                               # the swapped kernel at any size it takes
+            fast.SWAP_RULE = "always"                                               # the swapped kernel at any size it takes
         if a.kernel == "gemm_tc":
-            fast.ENABLED["gemm_tc_small"] = False                                   # the 128-row-tile kernel
+            fast.SWAP_RULE = "never"                                                # the tiled kernel
         if a.tile:
             rm, bn = a.tile.split("x")
             lib.cuda().axon_gemm_tc_force_tile(int(rm), int(bn))

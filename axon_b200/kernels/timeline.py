@@ -3,7 +3,8 @@
     python -m axon_b200.kernels.timeline decode  --batch 8 --context 2048 --layers 4
     python -m axon_b200.kernels.timeline prefill --tokens 2048 --layers 4
 
-Builds a model with the layer sizes of Qwen2.5-7B (random weights, ``--layers`` layers), runs
+Builds a model with the layer sizes of Qwen2.5-7B (``--shape`` for 1.5B or 32B; random weights,
+``--layers`` layers), runs
 a few steps, and prints for every kernel of the last one its start and end in microseconds
 after the step's first kernel, its duration, and how long after the end of the kernel
 before it it ended.  Under programmatic dependent launch a kernel starts early and waits
@@ -18,9 +19,16 @@ import sys
 
 import torch
 
-SIZES = dict(hidden_size=3584, intermediate_size=18944, num_attention_heads=28, num_key_value_heads=4,
-             vocab_size=152064, rms_norm_eps=1e-6, rope_theta=1000000.0, hidden_act="silu",
-             tie_word_embeddings=False, max_position_embeddings=32768)
+COMMON = dict(rms_norm_eps=1e-6, rope_theta=1000000.0, hidden_act="silu", max_position_embeddings=32768)
+#: layer sizes of the Qwen2.5 models by name
+SHAPES = {
+    "7b": dict(COMMON, hidden_size=3584, intermediate_size=18944, num_attention_heads=28, num_key_value_heads=4,
+               vocab_size=152064, tie_word_embeddings=False),
+    "1.5b": dict(COMMON, hidden_size=1536, intermediate_size=8960, num_attention_heads=12, num_key_value_heads=2,
+                 vocab_size=151936, tie_word_embeddings=True),
+    "32b": dict(COMMON, hidden_size=5120, intermediate_size=27648, num_attention_heads=40, num_key_value_heads=8,
+                vocab_size=152064, tie_word_embeddings=False),
+}
 
 
 def main() -> int:
@@ -30,18 +38,23 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="7b", help="whose layer sizes")
     ap.add_argument("--rows", type=int, default=60, help="kernels of the last step to print")
+    ap.add_argument("--swap-rule", choices=["model", "always", "never"], default="model",
+                    help="which products take the swapped kernel (kernels.fast.SWAP_RULE)")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         print("timeline needs a CUDA GPU", file=sys.stderr)
         return 2
     from torch.profiler import ProfilerActivity, profile
 
+    from . import fast
+    fast.SWAP_RULE = a.swap_rule
     from ..config import config_from_dict
     from ..engine.build import build_engine
     from ..engine.step import StepEntry
 
-    cfg = config_from_dict(dict(SIZES, num_hidden_layers=a.layers, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    cfg = config_from_dict(dict(SHAPES[a.shape], num_hidden_layers=a.layers, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
     room = max(a.context + 64, a.tokens + 64)
     slots = a.batch if a.kind == "decode" else 2
     engine = build_engine(config=cfg, seed=1, dtype="bfloat16", page_size=16, max_tokens=slots * (-(-room // 16) * 16),

@@ -411,7 +411,7 @@ def tile_shape(request):
 def test_gemm_tensor_core(ops, tile_shape, M, N, K, monkeypatch):
     """The tcgen05 kernel at sizes with tails in M, N and K, every epilogue, every tile shape."""
     from axon_b200.kernels import fast
-    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 64)          # the tiled kernel, also where the swapped one would run
+    monkeypatch.setattr(fast, "SWAP_RULE", "never")         # the tiled kernel, also where the swapped one would run
     a = rand(M, K, dtype=torch.bfloat16, seed=80)
     w = rand(N, K, dtype=torch.bfloat16, seed=81, std=0.1)
     bias = rand(N, seed=82)
@@ -447,8 +447,7 @@ def test_gemm_swapped_in_blocks_of_tokens(ops, M, N, K, monkeypatch):
     """The product with the tokens as the MMA's columns beyond 64 rows: 128 or 256 columns, and
     blocks of 256 tokens beyond that; every epilogue, split over K or not, folded by itself or by the reader."""
     from axon_b200.kernels import fast
-    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 1024)
-    monkeypatch.setattr(fast, "_takes_swapped_kernel", lambda m, n: True)
+    monkeypatch.setattr(fast, "SWAP_RULE", "always")
     a = rand(M, K, dtype=torch.bfloat16, seed=140)
     w = rand(N, K, dtype=torch.bfloat16, seed=141, std=0.1)
     bias = rand(N, seed=142)
@@ -482,7 +481,7 @@ def test_gemm_tensor_core_output_paths(ops, M, N, K, monkeypatch):
     """Outputs that TMA can address leave through shared memory and TMA (clipped at the edges, the
     residual by TMA's add); the others are stored from registers.  Both give the same numbers."""
     from axon_b200.kernels import fast, lib
-    monkeypatch.setattr(fast, "SWAP_MAX_ROWS", 64)
+    monkeypatch.setattr(fast, "SWAP_RULE", "never")
     a = rand(M, K, dtype=torch.bfloat16, seed=90)
     w = rand(N, K, dtype=torch.bfloat16, seed=91, std=0.1)
     bias = rand(N, seed=92)
