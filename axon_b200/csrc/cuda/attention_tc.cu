@@ -34,7 +34,7 @@ constexpr int AT_SOFTMAX_THREADS = AT_SUB * 128, AT_PRODUCERS = 64;
 constexpr int AT_MMA_WARP = AT_SOFTMAX_THREADS / 32;                   // warp 8
 constexpr int AT_PV_WARP = AT_MMA_WARP + 1 + AT_PRODUCERS / 32;        // warp 11
 constexpr int AT_THREADS = AT_SOFTMAX_THREADS + 32 + AT_PRODUCERS + 32; // 8 softmax warps, the Q K^T warp, 2 producer warps, the P V warp
-constexpr int AT_NK = 3, AT_NV = 3;              // stages of the key ring and of the value ring
+constexpr int AT_NK = 5, AT_NV = 5;              // stages of the key ring and of the value ring
 constexpr float AT_LAZY = 8.f;                   // log2 units a row's maximum may grow before O is rescaled
 
 struct AtParams {
@@ -122,14 +122,13 @@ attention_tc_kernel(const AtParams p) {
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(smem_dyn);
     constexpr uint32_t QSUB_BYTES = 2 * AT_BM * 128;            // a sub-tile: two halves [dims 0..63 | 64..127][row][64 dims]
     constexpr uint32_t KV_BYTES = 2 * AT_BN * 128;              // a tile: two halves [dims 0..63 | 64..127][key][64 dims]
-    constexpr uint32_t P_BYTES = AT_BM * 128;                   // [row][64 keys]
-    const uint32_t q_sm = base, k_sm = q_sm + AT_SUB * QSUB_BYTES, v_sm = k_sm + AT_NK * KV_BYTES, p_sm = v_sm + AT_NV * KV_BYTES;
-    const uint32_t bars = p_sm + 2 * AT_SUB * P_BYTES;          // two P buffers per sub-tile, used in turn
-    // mbarriers, 8 bytes each; s_full and s_free per (sub-tile, score buffer), p_full and pv_done per
-    // (sub-tile, P buffer): a wait by phase parity may lag its barrier by one phase only, and the
-    // softmax threads can be two tiles ahead of the thread that issues P V
+    const uint32_t q_sm = base, k_sm = q_sm + AT_SUB * QSUB_BYTES, v_sm = k_sm + AT_NK * KV_BYTES;
+    const uint32_t bars = v_sm + AT_NV * KV_BYTES;
+    // mbarriers, 8 bytes each; s_full, p_full and pv_done per (sub-tile, score buffer): a wait by
+    // phase parity may lag its barrier by one phase only, and the softmax threads can be two tiles
+    // ahead of the thread that issues P V
     const uint32_t k_full = bars, k_empty = k_full + 8 * AT_NK, v_full = k_empty + 8 * AT_NK, v_empty = v_full + 8 * AT_NV;
-    const uint32_t s_full = v_empty + 8 * AT_NV, s_free = s_full + 16 * AT_SUB, p_full = s_free + 16 * AT_SUB, pv_done = p_full + 16 * AT_SUB;
+    const uint32_t s_full = v_empty + 8 * AT_NV, p_full = s_full + 16 * AT_SUB, pv_done = p_full + 16 * AT_SUB;
     const uint32_t tmem_slot_addr = pv_done + 16 * AT_SUB;      // (pv_done: per sub-tile and P buffer)
     volatile uint32_t& tmem_slot = *reinterpret_cast<volatile uint32_t*>(smem_dyn + (tmem_slot_addr - base));
     // tensor memory: two score buffers of 64 columns per sub-tile in columns 0..255, O of the sub-tiles in 256..383 and 384..511
@@ -159,10 +158,7 @@ attention_tc_kernel(const AtParams p) {
         for (int g = 0; g < AT_SUB; ++g) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(s_full + 16 * g + 8 * b, 1);
-                mbar_init(s_free + 16 * g + 8 * b, 4);      // one arrival per softmax warp of the sub-tile
-            }
-            for (int b = 0; b < 2; ++b) {
-                mbar_init(p_full + 16 * g + 8 * b, 4);
+                mbar_init(p_full + 16 * g + 8 * b, 4);      // one arrival per softmax warp of the sub-tile
                 mbar_init(pv_done + 16 * g + 8 * b, 1);
             }
         }
@@ -271,12 +267,12 @@ attention_tc_kernel(const AtParams p) {
             };
 #pragma unroll 1
             for (int t = 0; t < n_tiles; ++t) {
-                // tile t's scores go to buffer t & 1, which the softmax threads gave back when they
-                // finished tile t - 2
+                // tile t's scores go to buffer t & 1, which held the scores and then P of tile t - 2:
+                // free once that tile's value product has read P
                 const int ks = t % AT_NK;
                 mbar_wait_idle(k_full + 8 * ks, (t / AT_NK) & 1, 1);
                 for (int g = 0; g < n_sub; ++g) {
-                    if (t >= 2) mbar_wait_idle(s_free + 16 * g + 8 * (t & 1), ((t - 2) >> 1) & 1, 1);
+                    if (t >= 2) mbar_wait_idle(pv_done + 16 * g + 8 * (t & 1), ((t - 2) >> 1) & 1, 1);
                     tc_fence_after();
                     issue_scores(g, t, k_sm + ks * KV_BYTES);
                 }
@@ -295,13 +291,13 @@ attention_tc_kernel(const AtParams p) {
                 for (int g = 0; g < n_sub; ++g) {
                     mbar_wait_idle(p_full + 16 * g + 8 * (i & 1), (i >> 1) & 1, 4);
                     tc_fence_after();
-                    const uint32_t pg = p_sm + (uint32_t)(2 * g + (i & 1)) * P_BYTES;
+                    // P lies in tensor memory, over the first half of the score buffer it came from
+                    const uint32_t pt = tmem + (uint32_t)((2 * g + (i & 1)) * AT_BN);
 #pragma unroll
                     for (int k = 0; k < AT_BN / TC_UMMA_K; ++k) {
-                        const uint64_t da = smem_desc(pg) + (uint64_t)(2 * k);
-                        // 16 keys = two groups of 8 along K: 2048 bytes further per step
+                        // 16 keys = two groups of 8 along K: 2048 bytes further per step; 8 columns of P
                         const uint64_t db = smem_desc_mn(vt + (uint32_t)k * 2048u, AT_BN * 128);
-                        umma(tmem + TMEM_O + (uint32_t)(g * AT_HD), da, db, idesc_o, (i | k) ? 1u : 0u);
+                        umma_ta(tmem + TMEM_O + (uint32_t)(g * AT_HD), pt + (uint32_t)(8 * k), db, idesc_o, (i | k) ? 1u : 0u);
                     }
                     umma_commit(pv_done + 16 * g + 8 * (i & 1));
                 }
@@ -315,7 +311,6 @@ attention_tc_kernel(const AtParams p) {
         const int R = g * AT_BM + row;                          // row of the whole tile
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tmem_o = tmem + TMEM_O + (uint32_t)(g * AT_HD) + lane_addr;
-        const uint32_t p_rows = p_sm + (uint32_t)(2 * g) * P_BYTES + (uint32_t)row * 128u;      // this row in the sub-tile's first P buffer
         const int my_pos = R < rows_used ? pos0 + R / p.group : -1;          // unused rows see no key
         const int my_lo = p.window > 0 ? my_pos - p.window + 1 : 0;
         // positions of the sub-tile's first and last used row: a tile all of them see whole needs no mask
@@ -377,35 +372,29 @@ attention_tc_kernel(const AtParams p) {
                 tmem_st_wait();
             }
             const float neg = m_use == -INFINITY ? 0.f : -m_use;
-            // P goes to the buffer that the product of the tile before the last has read
-            if (it > 1) mbar_wait(pv_done + 16 * g + 8 * (it & 1), ((it - 2) >> 1) & 1, 2);
-            const uint32_t p_row = p_rows + (uint32_t)(it & 1) * P_BYTES;
-            // ---- P = exp2(s - m) as bfloat16 into shared memory, and the row's sum
+            // ---- P = exp2(s - m) as bfloat16 back into tensor memory, over the first 32 columns of
+            // the scores it came from (a column holds two keys; the value product reads its A operand
+            // there), and the row's sum
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {            // 8 keys = one 16-byte chunk of the row of P
-                uint32_t pk[4];
+            for (int h = 0; h < 2; ++h) {            // keys 0..31, then 32..63: 16 columns of P each
+                uint32_t pk[16];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i = (8 * c + 2 * j) & 31;
-                    const float s0 = __uint_as_float(c < 4 ? sa[i] : sb[i]), s1 = __uint_as_float(c < 4 ? sa[i + 1] : sb[i + 1]);
+                for (int j = 0; j < 16; ++j) {
+                    const float s0 = __uint_as_float(h ? sb[2 * j] : sa[2 * j]), s1 = __uint_as_float(h ? sb[2 * j + 1] : sa[2 * j + 1]);
                     const float p0 = ex2(fmaf(s0, p.scale_log2, neg)), p1 = ex2(fmaf(s1, p.scale_log2, neg));
                     if (j & 1) { sum2 += p0; sum3 += p1; } else { sum0 += p0; sum1 += p1; }
                     __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                     pk[j] = *reinterpret_cast<uint32_t*>(&b);
                 }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row + (uint32_t)((c ^ (row & 7)) << 4)),
-                             "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]));
+                tmem_st16(tmem_s + (uint32_t)(16 * h), pk);
             }
             sum0 += sum2; sum1 += sum3;
             l += sum0 + sum1;
-            fence_async_proxy();                     // P (and a rescaled O) must be seen by the MMA
+            tmem_st_wait();                          // P (and a rescaled O) must be there before the MMA is told
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_free + 16 * g + 8 * (it & 1));       // the score buffer may take the tile after the next
-                mbar_arrive(p_full + 16 * g + 8 * (it & 1));
-            }
+            if (lane == 0) mbar_arrive(p_full + 16 * g + 8 * (it & 1));
         }
         mbar_wait(pv_done + 16 * g + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, 2);        // the last P V is done
         __syncwarp();
@@ -465,8 +454,8 @@ AXON_API int axon_attention_tc(const void* q, const void* pool, void* out, const
     p.kv = to_paged(layout);
     p.n_segments = n_segments; p.heads = heads; p.group = group; p.tokens_per_tile = tokens_per_tile; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    constexpr size_t smem = AT_SUB * 2 * AT_BM * 128 + (AT_NK + AT_NV) * (2 * AT_BN * 128) + 2 * AT_SUB * AT_BM * 128 +
-                            8 * (2 * AT_NK + 2 * AT_NV + 8 * AT_SUB) + 16;
+    constexpr size_t smem = AT_SUB * 2 * AT_BM * 128 + (AT_NK + AT_NV) * (2 * AT_BN * 128) +
+                            8 * (2 * AT_NK + 2 * AT_NV + 6 * AT_SUB) + 16;
     static_assert(smem <= 227 * 1024, "the tiles do not fit shared memory");
     if (p.kv.fault != nullptr) {
         if (int st = ensure_dynamic_smem<attention_tc_kernel<true>>(smem, "axon_attention_tc")) return st;

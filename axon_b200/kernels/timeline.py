@@ -42,6 +42,8 @@ def main() -> int:
     ap.add_argument("--rows", type=int, default=60, help="kernels of the last step to print")
     ap.add_argument("--swap-rule", choices=["model", "always", "never"], default="model",
                     help="which products take the swapped kernel (kernels.fast.SWAP_RULE)")
+    ap.add_argument("--disable", action="append", default=[], metavar="KERNEL",
+                    help="switch a tuned kernel off (a key of kernels.fast.ENABLED); may be repeated")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         print("timeline needs a CUDA GPU", file=sys.stderr)
@@ -50,6 +52,10 @@ def main() -> int:
 
     from . import fast
     fast.SWAP_RULE = a.swap_rule
+    for name in a.disable:
+        if name not in fast.ENABLED:
+            ap.error(f"--disable {name}: not one of {sorted(fast.ENABLED)}")
+        fast.ENABLED[name] = False
     from ..config import config_from_dict
     from ..engine.build import build_engine
     from ..engine.step import StepEntry
