@@ -68,6 +68,7 @@ _SIGNATURES = {
     "axon_gemm_tc_small": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_longlong, P, c_int, c_int, c_int,
                            ctypes.POINTER(c_int), P],
     "axon_gemm_prefers_swapped": [c_int, c_int, c_int, c_int, c_int],
+    "axon_mma_probe": [c_int, c_int, P, P, P],
     "axon_attention_fa": [P, P, P, P, c_int, P, c_int, ctypes.POINTER(KvLayout), c_int, c_float, c_int, c_int,
                           c_int, c_int, P, P, P],
     "axon_attention_fa_decode_fused": [P, P, c_int, c_int, P, P, c_int, P, P, P, c_int, ctypes.POINTER(KvLayout), c_int,

@@ -7,7 +7,10 @@ the algorithmic bytes and FLOPs, and the achieved rates.  The same command under
 ``ncu -k regex:<kernel>`` gives the counters of exactly that launch.
 
 Kernels: ``gemm_small_m``, ``gemm_tc``, ``attention_decode``, ``attention_prefill``,
-``rmsnorm``.
+``rmsnorm``; ``gemm_chain``: the swapped and the tiled product, each as a captured chain of
+launches over distinct weights (as the layers of a step follow one another), which is what the
+rule that chooses between them was fitted to; and ``mma_probe``: the cycles an SM's tensor pipe spends per 64-key step on the
+products of the prompt attention when nothing else holds them up (``csrc/cuda/mma_probe.cu``).
 """
 
 from __future__ import annotations
@@ -73,7 +76,7 @@ def _ctx(segs, items=True):
 
 def main() -> int:
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attention_decode", "attention_prefill", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm_small_m", "gemm_tc", "attention_decode", "attention_prefill", "rmsnorm", "mma_probe", "gemm_chain"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=37888)
     ap.add_argument("--k", type=int, default=3584)
@@ -89,6 +92,7 @@ def main() -> int:
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--target-ctas", type=int, default=0, help="gemm_small_m: CTAs the split-K aims at")
     ap.add_argument("--tile", default="", help="gemm_tc: force the tile shape, e.g. 2x256 (rows/128 x columns)")
+    ap.add_argument("--rows", default="64,128,256,512", help="gemm_chain: row counts, comma-separated")
     ap.add_argument("--mma-sync", action="store_true", help="attention_prefill: the mma.sync kernel, not the tcgen05 one")
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -98,6 +102,58 @@ def main() -> int:
     g = torch.Generator(device=DEV).manual_seed(0)
     flush = not a.no_flush
 
+    if a.kernel == "mma_probe":
+        import ctypes
+        scratch = torch.zeros(2, dtype=torch.int64, device=DEV)
+        cycles = (ctypes.c_ulonglong * 2)()
+        steps = 1000
+        rows = {}
+        for what, name in ((1, "scores (M 128, N 64, K 16; 16 a step)"), (2, "values, P in shared memory, V MN-major (8 a step)"),
+                           (3, "both, P in shared memory"), (4, "values, P in tensor memory"), (5, "both, P in tensor memory")):
+            fast.check(lib.cuda().axon_mma_probe(what, steps, scratch.data_ptr(), cycles, fast._stream()))
+            rows[name] = {"scores_thread_cycles_per_step": round(cycles[0] / steps, 1), "values_thread_cycles_per_step": round(cycles[1] / steps, 1)}
+            print(f"{name:56s} scores thread {cycles[0] / steps:7.1f}  values thread {cycles[1] / steps:7.1f}  cycles per step")
+        print(json.dumps({"kernel": "mma_probe", "steps": steps, "math_cycles_per_step": 1024, "rows": rows}))
+        return 0
+    if a.kernel == "gemm_chain":
+        epi = {"store": fast.EPI_STORE_F32, "residual": fast.EPI_RESIDUAL, "swiglu": fast.EPI_SWIGLU, "bf16": fast.EPI_STORE_BF16}[a.epilogue]
+        copies = max(6, min(40, (300 << 20) // (a.n * a.k * 2) + 1))          # more weights than L2 holds
+        ws = [(torch.randn(a.n, a.k, generator=g, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        scrub = torch.empty(L2_BYTES, dtype=torch.uint8, device=DEV)
+        side = torch.cuda.Stream()
+        rows = {}
+        for m in [int(v) for v in a.rows.split(",")]:
+            x = torch.randn(m, a.k, generator=g, device=DEV).to(torch.bfloat16)
+            out = (torch.empty(m, a.n // 2, dtype=torch.bfloat16, device=DEV) if a.epilogue == "swiglu" else
+                   torch.zeros(m, a.n, dtype=torch.bfloat16 if a.epilogue == "bf16" else torch.float32, device=DEV))
+            swapped = lambda w: fast._gemm_small(x, w, None, out, epi, m, a.n, a.k)
+            tiled = lambda w: fast.check(lib.cuda().axon_gemm_tc(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), epi, m, a.n, a.k,
+                                                                 out.stride(0), fast._stream()))
+            got = {}
+            for name, launch in (("swapped", swapped), ("tiled", tiled)):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    launch(ws[0])
+                    torch.cuda.synchronize()
+                    with torch.cuda.graph(graph, stream=side):
+                        for w in ws:
+                            launch(w)
+                times = []
+                for _ in range(a.iters):
+                    scrub.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    graph.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1) * 1e3 / copies)
+                got[name] = round(statistics.median(times[1:] or times), 1)
+            got["rule_takes"] = "swapped" if fast._takes_swapped_kernel(m, a.n, a.k) else "tiled"
+            rows[m] = got
+            print(f"rows {m:5d}: swapped {got['swapped']:8.1f} us   tiled {got['tiled']:8.1f} us   (the rule takes the {got['rule_takes']} one)")
+        print(json.dumps({"kernel": "gemm_chain", "n": a.n, "k": a.k, "epilogue": a.epilogue, "weights_in_chain": copies, "us_per_launch": rows}))
+        assert fast.gemm_tc_status() == 0
+        return 0
     if a.kernel in ("gemm_small_m", "gemm_tc"):
         x = torch.randn(a.m, a.k, generator=g, device=DEV).to(torch.bfloat16)
         w = (torch.randn(a.n, a.k, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
