@@ -764,8 +764,8 @@ AXON_API void axon_gemm_tc_force_tile(int rm, int bn) { g_force_rm = rm; g_force
 // cannot address do.
 AXON_API void axon_gemm_tc_force_plain_out(int on) { g_force_plain_out = on; }
 
-// a [M][K], w [N][K] bfloat16, contiguous, K % 8 == 0, 16-byte aligned.  Epilogues as in
-// axon_gemm_small_m: 0 float out, 1 bfloat16 out, 2 out += (float), 3 SwiGLU to bfloat16 [M][N/2].
+// a [M][K], w [N][K] bfloat16, contiguous, K % 8 == 0, 16-byte aligned.  Epilogues:
+// 0 float out, 1 bfloat16 out, 2 out += (float), 3 SwiGLU to bfloat16 [M][N/2].
 AXON_API int axon_gemm_tc(const void* a, const void* w, const float* bias, void* out, int epilogue, int M, int N,
                           int K, int ldo, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return AXON_OK;
