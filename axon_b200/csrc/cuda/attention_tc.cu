@@ -13,10 +13,13 @@
 //                         score buffers in tensor memory, a tile ahead of the softmax; the other
 //                         O += P V_i (M 128, N 128, K 64, V read MN-major as it lies in the cache)
 //                         as soon as P is there; mbarriers (tcgen05.commit) tell the others;
-//   softmax (2 x 4 warps) a thread per row reads its 64 scores (tcgen05.ld), frees the score
-//                         buffer at once, masks per element where the tile is not seen whole
-//                         (causal, window), keeps a running maximum and sum, and writes
-//                         P = exp2(s - m) as bfloat16 in operand layout to shared memory.
+//   softmax (2 x 4 warps) a thread per row reads its 64 scores (tcgen05.ld), masks per element
+//                         where the tile is not seen whole (causal, window), keeps a running
+//                         maximum and sum, and writes P = exp2(s - m) as bfloat16 back into
+//                         tensor memory (tcgen05.st) over the first half of the scores it came
+//                         from, where the value product reads it as its A operand: P never
+//                         passes through shared memory, and the score buffer is free for the
+//                         tile after the next once that value product is done.
 //
 // While one sub-tile's threads compute exponentials, the tensor pipe works on the other's
 // products; neither waits for the gather.  The maximum m that the exponent uses lags the true
