@@ -927,3 +927,19 @@ def test_pickers_read_rows_by_index(ops):
     got = torch.empty(3, vocab, device=DEV)
     ops.gather_rows(logits, idx, got)
     assert torch.equal(got, sub)
+
+
+def test_tensor_pipe_probe_times_the_attention_products(ops):
+    """The measuring kernel of ``microbench mma_probe``: both issuing threads finish, no wait gives
+    up, and a step of score products takes at least its 512 cycles of arithmetic and not ten
+    times as long."""
+    import ctypes
+    from axon_b200.kernels import fast, lib
+    scratch = torch.zeros(2, dtype=torch.int64, device=DEV)
+    cycles = (ctypes.c_ulonglong * 2)()
+    steps = 200
+    fast.check(lib.cuda().axon_mma_probe(1, steps, scratch.data_ptr(), cycles, fast._stream()))
+    assert 512 <= cycles[0] / steps <= 5120 and cycles[1] == 0
+    fast.check(lib.cuda().axon_mma_probe(5, steps, scratch.data_ptr(), cycles, fast._stream()))
+    assert cycles[0] / steps >= 1024 and cycles[1] / steps >= 1024
+    assert lib.cuda().axon_mma_probe(1, 0, scratch.data_ptr(), cycles, fast._stream()) != 0      # refused: no steps
