@@ -245,6 +245,32 @@ def test_long_decoding(model_folders, plain_models, name, dtype, n):
     check_rows(rows, list(want), TOL[dtype], f"{name}/{dtype} {n} tokens one by one")
 
 
+@pytest.mark.parametrize("name,dtype", [("C", "bfloat16"), ("C", "float32"), ("B", "bfloat16"), ("D", "bfloat16")])
+def test_pages_far_apart_in_a_pool_beyond_four_gib(model_folders, plain_models, name, dtype):
+    """A pool of 2**32 elements (8 or 16 GiB) with pages handed out in shuffled
+    order: a request's pages lie gigabytes apart, so every paged kernel's offsets (prompt and
+    decode attention, the cache writes) have to be 64-bit.  A prompt whole, then tokens one by one."""
+    cfg = TINY[name]
+    per_token = cfg["num_hidden_layers"] * 2 * cfg["num_key_value_heads"] * cfg["head_dim"]
+    pool_tokens = -(-(2**32) // per_token // 16) * 16            # half of the pages lie beyond 2**31 elements
+    engine = build(model_folders[name], dtype, max_tokens=pool_tokens, page_size=16, shuffle_seed=11)
+    assert engine.cache.groups[0].pool.numel() > 2**31
+    n_prompt, n_dec = PROMPT_LENGTHS[name][3], 24
+    toks = tokens_for(name, 9, n_prompt + n_dec)
+    cfg_w = plain_models[name]
+    want = plain.forward(cfg_w[0], cfg_w[1], toks)
+    tr = Trace()
+    tr.step([("r", ("x",), toks[:n_prompt], range(n_prompt))])
+    for t in range(n_prompt, n_prompt + n_dec):
+        tr.step([("r", ("x",), [toks[t]], [0])])
+    got = replay(engine, tr.steps)
+    table = engine.cache.manager.table(0)[0]
+    used = [int(p) for p in table[: -(-(n_prompt + n_dec) // 16)]]
+    assert max(used) * 16 * per_token > 2**31, "the shuffle left this request's pages in the first gigabytes"
+    rows = torch.cat([got[k] for k in range(len(tr.steps))])
+    check_rows(rows, list(want), TOL[dtype], f"{name}/{dtype} in a pool of {pool_tokens} positions")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_first_tokens_of_a_sequence(model_folders, plain_models, name, dtype):
