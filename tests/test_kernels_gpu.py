@@ -674,6 +674,7 @@ def test_attention_tensor_core(ops, heads, kv_heads, hd, ps, window, fold, tcgen
     (12, 2, 8, 200, [(700, 700), (90, 1000)]),                   # a window: tiles wholly inside it, at its edges, before it
     (3, 3, 32, 0, [(260, 260), (5, 400)]),                       # one head per kv head: 128 tokens a tile
     (64, 1, 16, 0, [(70, 200)]),                                 # 64 heads to a kv head: two tokens a tile
+    (8, 2, 16, 0, [(6000, 6000), (200, 9000)]),                  # more CTAs than SMs, 140 key tiles: every ring and barrier wraps many times
 ])
 def test_attention_tcgen05_prompts(ops, heads, kv_heads, ps, window, shapes):
     """The tcgen05 kernel for prompt portions (head size 128) over several key tiles, against
@@ -724,6 +725,55 @@ def test_attention_tcgen05_prompts(ops, heads, kv_heads, ps, window, shapes):
                 assert w[-1].max() > 0.5, "the planted key does not stand out"
             close(out.view(-1, heads, hd)[at:at + n, h], w @ vs[s][:, h // group].double(), 1.5e-2,
                   f"request {s} head {h}")
+        at += n
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,window", [(28, 4, 128, 0), (6, 2, 64, 0), (8, 8, 128, 5000)])
+def test_decode_attention_at_long_contexts(ops, heads, kv_heads, hd, window):
+    """Decoded tokens at contexts of thousands of positions (many key splits, hundreds of tiles a
+    share, block-table rows of two thousand entries), against float64; one key far back gets a
+    large score."""
+    from axon_b200.kernels import fast
+    ps = 16
+    shapes = [(1, 20000), (1, 33000), (2, 8191), (1, 4097)]
+    max_pos = max(kv for _, kv in shapes)
+    slots = len(shapes)
+    view, table = make_cache(ops, torch.bfloat16, kv_heads, hd, ps, slots * -(-max_pos // ps), slots, max_pos,
+                             window=window, seed=29)
+    group = heads // kv_heads
+    ks, vs = [], []
+    for s, (n, kv_len) in enumerate(shapes):
+        k = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=800 + s)
+        v = rand(kv_len, kv_heads, hd, dtype=torch.bfloat16, seed=900 + s)
+        ks.append(k); vs.append(v)
+        pages = table[s, : -(-kv_len // ps)].long()
+        pad = len(pages) * ps - kv_len
+        for which, t in ((0, k), (1, v)):
+            t = torch.cat([t, torch.zeros(pad, kv_heads, hd, dtype=t.dtype, device=DEV)])
+            view.pool[pages, view.entry, which] = t.view(len(pages), ps, kv_heads, hd).permute(0, 2, 1, 3)
+    ctx = _ctx_for([(s, n, kv_len) for s, (n, kv_len) in enumerate(shapes)])
+    q = rand(ctx.n_tokens, heads * hd, dtype=torch.bfloat16, seed=77)
+    qv = q.view(ctx.n_tokens, heads, hd)
+    at = 0
+    for s, (n, kv_len) in enumerate(shapes):
+        far = max(0, kv_len - window) if window else 7
+        for h in range(heads):
+            qv[at + n - 1, h] = (ks[s][far, h // group].float() * (8.0 / math.sqrt(hd) if hd < 128 else 1.5)).to(torch.bfloat16)
+        at += n
+    out = torch.zeros_like(q)
+    scale = 1.0 / math.sqrt(hd)
+    assert fast.attention(q, view, ctx, out, heads, scale)
+    at = 0
+    for s, (n, kv_len) in enumerate(shapes):
+        qpos = torch.arange(kv_len - n, kv_len, device=DEV)[:, None]
+        kpos = torch.arange(kv_len, device=DEV)[None, :]
+        mask = kpos <= qpos
+        if window:
+            mask &= kpos > qpos - window
+        for h in range(heads):
+            sc = (qv[at:at + n, h].double() @ ks[s][:, h // group].double().T) * scale
+            w = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1)
+            close(out.view(-1, heads, hd)[at:at + n, h], w @ vs[s][:, h // group].double(), 1.5e-2, f"request {s} head {h}")
         at += n
 
 
