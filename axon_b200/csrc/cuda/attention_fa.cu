@@ -25,7 +25,7 @@ namespace axon {
 
 constexpr int FA_BN = 64;       // keys per tile
 constexpr int FA_THREADS = 128; // 4 warps
-constexpr int FA_MAX_SPLITS = 32;
+constexpr int FA_MAX_SPLITS = 64;
 
 struct FaParams {
     const __nv_bfloat16* q;      // [tokens][heads * hd]

@@ -179,7 +179,7 @@ def gemm_swiglu(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> 
 
 
 FA_HEAD_DIMS = (16, 32, 64, 128)
-FA_MAX_SPLITS = 32
+FA_MAX_SPLITS = 64
 #: CTAs the decode attention never exceeds when it splits the keys of each request: two CTAs fit
 #: an SM, and a launch that spills into a second wave pays for it (measured at 7B sizes: 320 CTAs
 #: at batch 16 cost 10 % of the step against 256)

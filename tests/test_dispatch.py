@@ -21,6 +21,8 @@ def test_decode_attention_never_starts_more_ctas_than_fit():
     # between 32 and 37 requests two shares still fit at once, and halve the longest CTA
     assert fast.decode_split_count(36, 4, 2048) == 2 and fast.decode_split_count(24, 4, 2048) == 3
     assert fast.decode_split_count(38, 4, 2048) == 1
+    # one request at a long context: up to 64 shares (128 CTAs of 16 tiles left half the machine idle)
+    assert fast.decode_split_count(1, 4, 32768) == 57 and fast.decode_split_count(2, 4, 32768) == 37
 
 
 def test_which_products_take_the_swapped_kernel():
