@@ -11,7 +11,9 @@
 namespace axon {
 
 // what: bit 0 score products; bit 1 value products with P in shared memory and V MN-major (as V
-// lies in the cache); bit 2 the same with P in tensor memory.
+// lies in the cache); bit 2 the same with P in tensor memory; bit 3 products of the value
+// products' shape (M 128, N 128, K 16, 8 a step) with both operands K-major from shared memory
+// (the queries against 128 keys), to tell the operand layout's share of their time.
 __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int steps, int what, unsigned long long* cycles) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = ((uint32_t)__cvta_generic_to_shared(smem_dyn) + 1023u) & ~1023u;
@@ -52,6 +54,19 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int steps, int what, 
     // values: three stages; P: two tiles of 16 KB
     const uint32_t q_sm = base, k_sm = base + 65536, v_sm = k_sm + 3 * 16384, p_sm = v_sm + 3 * 16384;
     const long long t0 = clock64();
+    if (lane == 0 && warp == 2 && (what & 8)) {
+        for (int t = 0; t < steps; ++t) {
+            for (int g = 0; g < 2; ++g) {
+                const uint32_t qg = q_sm + (uint32_t)g * 32768;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)           // half a head's dimensions: 4 MMAs, as a value product of 64 keys has
+                    umma(tmem + 256 + (uint32_t)(g * 128), smem_desc(qg) + (uint64_t)(2 * k), smem_desc(k_sm) + (uint64_t)(2 * k), instr_desc(128, 128), (t | k) ? 1u : 0u);
+            }
+        }
+        umma_commit(bar0 + 8);
+        mbar_wait(bar0 + 8, 0, 1);
+        if (blockIdx.x == 0) cycles[1] = (unsigned long long)(clock64() - t0);
+    }
     if (lane == 0 && warp == 0 && (what & 1)) {
         // (where the value products read P from tensor memory the scores land over it, as in the
         // kernel, and P is then 128.0 and 0.0 instead of 0.5: ordinary numbers either way)

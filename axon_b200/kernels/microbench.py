@@ -109,7 +109,8 @@ def main() -> int:
         steps = 1000
         rows = {}
         for what, name in ((1, "scores (M 128, N 64, K 16; 16 a step)"), (2, "values, P in shared memory, V MN-major (8 a step)"),
-                           (3, "both, P in shared memory"), (4, "values, P in tensor memory"), (5, "both, P in tensor memory")):
+                           (3, "both, P in shared memory"), (4, "values, P in tensor memory"), (5, "both, P in tensor memory"),
+                           (8, "the values' shape with both operands K-major")):
             fast.check(lib.cuda().axon_mma_probe(what, steps, scratch.data_ptr(), cycles, fast._stream()))
             rows[name] = {"scores_thread_cycles_per_step": round(cycles[0] / steps, 1), "values_thread_cycles_per_step": round(cycles[1] / steps, 1)}
             print(f"{name:56s} scores thread {cycles[0] / steps:7.1f}  values thread {cycles[1] / steps:7.1f}  cycles per step")
